@@ -1,0 +1,378 @@
+#!/usr/bin/env python3
+"""Benchmark of the fused GEMM+bias+GELU hot path (headline) with the INT8 GEMM
+and the softmax+dropout kernel measured beside it.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One JSON line on stdout (rank 0).  A step is one pass of the hot path over one
+batch of synthetic input:
+  headline  FP16 GEMM+bias+GELU at the BERT-large FFN-up shape, M 16384 (32 x 512
+            tokens), K 1024, N 4096, FP32 accumulate -> TFLOPS (2*M*N*K per step)
+  value     device-resident inputs, CUDA events around exactly K steps
+  e2e       the same step through the host-buffer operator of the library
+            (pinned host operands, H2D of A/B/bias and D2H of C inside the timing)
+  N > 1     one process per GPU (torchrun), every rank runs the full-size step on
+            its own tokens with replicated weights: weak scaling, no collective on
+            the data path; time = max over ranks.
+--impl reference times the CPU restatement of the reference's own computation
+(oracle/) on the host cores over a bounded row sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M, K, N = 16384, 1024, 4096
+FLOP_PER_STEP = 2.0 * M * N * K
+NOMINAL = {"fp16_tflops": 2250.0, "int8_tops": 4500.0, "hbm_gbs": 8000.0}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"],
+                "tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.thr = threading.Thread(target=self._read, daemon=True)
+            self.thr.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for (_, l) in self.lines]
+        mhz, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                mhz.append(float(f[1])); mx = float(f[2])
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        mhz.sort()
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(mhz)}
+
+
+# --------------------------------------------------------------- reference arm
+def cpu_gemm_sample(seconds_target: float = 12.0):
+    """Times the oracle's FP16 GEMM+bias+GELU loop (all host threads) on the first
+    rows of the same workload; returns (tflops, rows, seconds, threads)."""
+    from oracle import oracle
+    from tensorfuse_b200 import workloads
+    import numpy as np
+    A, B, b = workloads.gemm_fp16_ffn(M=2048)      # same generator, first 2048 rows
+    threads = oracle.max_threads()
+    pilot = 64
+    t = time.perf_counter(); oracle.gemm_bias_gelu_f16(A[:pilot], B, b); dt = time.perf_counter() - t
+    rows = int(min(2048, max(pilot, pilot * seconds_target / max(dt, 1e-6))))
+    rows = max(threads, rows // threads * threads)
+    t = time.perf_counter(); out = oracle.gemm_bias_gelu_f16(A[:rows], B, b); dt = time.perf_counter() - t
+    assert np.isfinite(out.astype(np.float32)).all()
+    return 2.0 * rows * N * K / dt / 1e12, rows, dt, threads
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    per_step = max(1.0, min(12.0, 120.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_gemm_sample(per_step)
+    vals, rows, secs = [], 0, 0.0
+    for _ in range(args.steps):
+        v, rows, dt, threads = cpu_gemm_sample(per_step)
+        vals.append(v); secs += dt
+    value = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "fp16_gemm_bias_gelu_tflops", "value": value, "unit": "TFLOPS",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "fp16_gemm_bias_gelu_bert_large_ffn_up", "M": M, "K": K, "N": N,
+                   "sample": f"first {rows} of {M} rows per step"},
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": threads, "kind": "port",
+                         "sample": f"first {rows} of {M} rows, all {N} columns, full K; C loops of the oracle, "
+                                   f"{threads} OpenMP threads"},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ---------------------------------------------------------------- GPU arm
+def run_gpu(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import tensorfuse_b200 as tf
+    from tensorfuse_b200 import workloads
+    from tensorfuse_b200._lib import lib as L
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    tf.init()
+    dev = torch.device("cuda", local)
+    peaks = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- operands: per-rank tokens (seed offset by rank), replicated weights
+    A_h, B_h, b_h = workloads.gemm_fp16_ffn(seed=1)          # rank 0: config 2 exactly
+    if rank > 0:                                             # other ranks: their own tokens, same weights
+        A_h = workloads.gemm_fp16_ffn(seed=1 + 1000 * rank)[0]
+    SETS = 4   # rotating operand sets: 4 x (33.6 MB A + 134 MB C) > 126 MB L2
+    dA = [torch.from_numpy(A_h).to(dev) if i == 0 else torch.from_numpy(np.roll(A_h, i, axis=0)).to(dev) for i in range(SETS)]
+    dB = torch.from_numpy(B_h).to(dev)
+    db = torch.from_numpy(b_h).to(dev)
+    dC = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(SETS)]
+    stream = torch.cuda.current_stream()
+    sp = int(stream.cuda_stream)
+
+    def step(i):
+        s = i % SETS
+        st = L.fused_gemm_bias_gelu_fp16_wrapper(dA[s].data_ptr(), dB.data_ptr(), db.data_ptr(), dC[s].data_ptr(),
+                                                 M, N, K, 1.0, 1.0, sp)
+        if st != 0:
+            raise RuntimeError("fused_gemm_bias_gelu_fp16_wrapper: " + tf.get_error_string(st))
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    launches0 = tf.launch_count()
+    barrier()
+    t_wall0 = time.time()
+    evs[0].record(stream)
+    for i in range(args.steps):
+        step(i)
+        evs[i + 1].record(stream)
+    torch.cuda.synchronize()
+    t_wall1 = time.time()
+    launches = tf.launch_count() - launches0
+    barrier()
+    total_ms = max_over_ranks(evs[0].elapsed_time(evs[-1]))
+    per = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps))
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    assert tf.watchdog_status() == 0, "a bounded device-side wait expired"
+    ms_per_step = total_ms / args.steps
+    value = world * FLOP_PER_STEP / (ms_per_step * 1e-3) / 1e12
+    kernel_ms = sum(per) / len(per)            # one launch per step on this stream
+    achieved = FLOP_PER_STEP / (kernel_ms * 1e-3) / 1e12
+
+    # ---- end to end: host operands (pinned), copies inside the timed region
+    pA = tf.pinned_empty((M, K), np.float16); pA[...] = A_h
+    pB = tf.pinned_empty((K, N), np.float16); pB[...] = B_h
+    pb = tf.pinned_empty((N,), np.float16); pb[...] = b_h
+    pC = tf.pinned_empty((M, N), np.float16)
+    e2e_steps = max(3, min(args.steps, 20))
+    for _ in range(2):
+        tf.fused_gemm_bias_gelu(pA, pB, pb, pC)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        tf.fused_gemm_bias_gelu(pA, pB, pb, pC)
+        _ = float(pC[0, 0])                    # the result is on the host
+    torch.cuda.synchronize()
+    e2e_s = max_over_ranks(time.perf_counter() - t0) / e2e_steps
+    e2e_val = world * FLOP_PER_STEP / e2e_s / 1e12
+    h2d = pA.nbytes + pB.nbytes + pb.nbytes
+    d2h = pC.nbytes
+
+    others = {}
+    cpu = None
+    if rank == 0:
+        others = side_workloads(tf, L, dev, peaks, args)
+        if world == 1:
+            v, rows, dt, threads = cpu_gemm_sample(12.0)
+            cpu = {"value": v, "unit": "TFLOPS", "cores": threads, "kind": "port",
+                   "sample": f"first {rows} of {M} rows, all {N} columns, full K ({dt:.1f} s); C loops of the "
+                             f"oracle restating the reference's CPU reference computation, {threads} OpenMP threads"}
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return 0
+    line = {
+        "metric": "fp16_gemm_bias_gelu_tflops", "value": value, "unit": "TFLOPS", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "fp16_gemm_bias_gelu_bert_large_ffn_up", "M_per_gpu": M, "K": K, "N": N,
+                   "accumulate": "f32", "parallelism": f"dp{world}_row_sharded_replicated_weights",
+                   "l2": f"{SETS} rotating operand sets (A+C {SETS * (A_h.nbytes + M * N * 2) >> 20} MiB) > 126 MB L2, no flush"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": achieved / peaks["tflops"], "traffic": None,
+                     "peak_source": f"{peaks['source']} bf16 cuBLAS burst (MEASURED_PEAKS.json)",
+                     "frac_of_nominal_2250": achieved / NOMINAL["fp16_tflops"],
+                     "kernel_ms_avg": kernel_ms, "kernel_ms_min": per[0]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_val, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_s * 1e3, "api": "tensorfuse_b200.fused_gemm_bias_gelu(numpy) -> "
+                                                   "tensorfuse_b200_gemm_bias_gelu_host"},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "other_workloads": others,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def side_workloads(tf, L, dev, peaks, args):
+    """INT8 GEMM (config 3) and softmax+dropout (config 4) on rank 0, same protocol."""
+    import numpy as np
+    import torch
+    out = {}
+    stream = torch.cuda.current_stream(); sp = int(stream.cuda_stream)
+    steps = max(5, min(args.steps, 20))
+
+    def timed(fn, n):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        e[0].record(stream)
+        for i in range(n):
+            fn(i); e[i + 1].record(stream)
+        torch.cuda.synchronize()
+        per = sorted(e[i].elapsed_time(e[i + 1]) for i in range(n))
+        return sum(per) / n, per[0]
+
+    # --- softmax + dropout, 32x16x512x512 FP16: 5 bytes per element
+    try:
+        rows, Lr = 32 * 16 * 512, 512
+        sets = 2   # 2 x (268 + 268 + 134 MB) > L2
+        g = torch.Generator(device=dev); g.manual_seed(3)
+        xs = [(torch.randn((rows, Lr), generator=g, device=dev) / 8).half() for _ in range(sets)]
+        os_ = [torch.empty_like(x) for x in xs]
+        ms_ = [torch.empty((rows, Lr), dtype=torch.uint8, device=dev) for _ in range(sets)]
+        for p in (0.0, 0.1):
+            def fn(i, p=p):
+                s = i % sets
+                st = L.tensorfuse_b200_softmax_dropout_rows(xs[s].data_ptr(), os_[s].data_ptr(), ms_[s].data_ptr(),
+                                                            rows, Lr, 1, p, 3, 0, sp)
+                assert st == 0
+            avg, best = timed(fn, steps)
+            gbs = rows * Lr * 5 / (avg * 1e-3) / 1e9
+            out[f"softmax_dropout_fp16_p{p}"] = {
+                "metric": "softmax_dropout_hbm_gbs", "value": gbs, "unit": "GB/s", "ms": avg, "ms_min": best,
+                "workload": "32x16x512x512 FP16 scores, 5 B/element (2 read + 2 write + 1 mask)",
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": gbs / peaks["hbm_gbs"], "frac_of_nominal_8000": gbs / NOMINAL["hbm_gbs"]}}
+        del xs, os_, ms_
+    except Exception as e:  # keep the headline line even if a side workload fails
+        out["softmax_dropout_error"] = repr(e)
+
+    # --- INT8 GEMM + dequant + bias + GELU, M 8192 K 4096 N 16384, FP16 out
+    try:
+        Mi, Ki, Ni = 8192, 4096, 16384
+        A = torch.randint(-127, 128, (Mi, Ki), dtype=torch.int8, device=dev)
+        B = torch.randint(-127, 128, (Ki, Ni), dtype=torch.int8, device=dev)
+        bias = (torch.randn(Ni, device=dev) * 0.02).half()
+        C = torch.empty((Mi, Ni), dtype=torch.float16, device=dev)
+        def fn(i):
+            st = L.tensorfuse_b200_gemm_int8(A.data_ptr(), B.data_ptr(), bias.data_ptr(), C.data_ptr(), Mi, Ni, Ki,
+                                             1e-2, 1e-4, 1, 1, 1, sp)
+            assert st == 0
+        avg, best = timed(fn, steps)
+        tops = 2.0 * Mi * Ni * Ki / (avg * 1e-3) / 1e12
+        int8_peak = None
+        try:
+            a2 = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device=dev)
+            b2 = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device=dev).t().contiguous().t()
+            f2 = lambda i: torch._int_mm(a2, b2)
+            pavg, pbest = timed(f2, 10)
+            int8_peak = 2.0 * 8192 ** 3 / (pbest * 1e-3) / 1e12
+        except Exception:
+            pass
+        out["int8_gemm_dequant_bias_gelu"] = {
+            "metric": "int8_gemm_bias_gelu_tops", "value": tops, "unit": "TOPS", "ms": avg, "ms_min": best,
+            "workload": "M 8192 K 4096 N 16384, INT32 accumulate, FP16 bias/out (operands resident, 604 MB > L2)",
+            "roofline": {"bound": "tensor", "achieved": tops, "peak": int8_peak, "unit": "TOP/s",
+                         "frac": (tops / int8_peak) if int8_peak else None,
+                         "peak_source": "torch._int_mm 8192^3 best of 10, measured in this run",
+                         "frac_of_nominal_4500": tops / NOMINAL["int8_tops"]}}
+    except Exception as e:
+        out["int8_gemm_error"] = repr(e)
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="tensorfuse_b200", choices=["tensorfuse_b200", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_gpu(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

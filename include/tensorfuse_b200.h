@@ -1,0 +1,144 @@
+/* tensorfuse_b200.h -- flat-pointer entry points of libtensorfuse.so.
+ *
+ * Part 1 are the C symbols the reference's benchmarks and C++ tests bind
+ * (plain device pointers and sizes); part 2 are additions of this build.
+ */
+#ifndef TENSORFUSE_B200_H_
+#define TENSORFUSE_B200_H_
+
+#include "tensorfuse/types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ part 1
+ * C = gelu(alpha * A[M,K] * B[K,N] + beta * bias[N]); all row-major device
+ * memory, bias and C of the operand type.
+ * reference declarations benchmarks/tensorfuse_c_api.h:44-52, definitions
+ * src/kernels/fused_gemm_bias_gelu.cu:352-370 (fp32/fp16),
+ * src/kernels/fused_gemm_bias_gelu_optimized.cu:314-328 (optimized_*). */
+TensorFuseStatus fused_gemm_bias_gelu_fp32_wrapper(const void* A, const void* B, const void* bias,
+                                                   void* C, int M, int N, int K, float alpha,
+                                                   float beta, cudaStream_t stream);
+TensorFuseStatus fused_gemm_bias_gelu_fp16_wrapper(const void* A, const void* B, const void* bias,
+                                                   void* C, int M, int N, int K, float alpha,
+                                                   float beta, cudaStream_t stream);
+TensorFuseStatus optimized_fused_gemm_bias_gelu_fp32_wrapper(const void* A, const void* B,
+                                                             const void* bias, void* C, int M,
+                                                             int N, int K, float alpha, float beta,
+                                                             cudaStream_t stream);
+TensorFuseStatus optimized_fused_gemm_bias_gelu_fp16_wrapper(const void* A, const void* B,
+                                                             const void* bias, void* C, int M,
+                                                             int N, int K, float alpha, float beta,
+                                                             cudaStream_t stream);
+
+/* INT8 operands, FP32 bias, FP32 output, the reference's scale convention
+ * (scale = 127/max|x|): C = gelu_clamped(acc/(scale_A*scale_B) + bias) * (scale_A*scale_B),
+ * non-finite results replaced by 0; alpha and beta are accepted and, as in the
+ * reference, have no effect.  The variant without scales uses 1, 1.
+ * reference src/kernels/fused_gemm_bias_gelu_int8.cu:364-378 */
+TensorFuseStatus fused_gemm_bias_gelu_int8_wrapper(const void* A, const void* B, const void* bias,
+                                                   void* C, int M, int N, int K, float alpha,
+                                                   float beta, cudaStream_t stream);
+TensorFuseStatus fused_gemm_bias_gelu_int8_wrapper_with_scales(const void* A, const void* B,
+                                                               const void* bias, void* C, int M,
+                                                               int N, int K, float alpha, float beta,
+                                                               float scale_A, float scale_B,
+                                                               cudaStream_t stream);
+
+/* Softmax over the innermost axis of a [batch, num_heads, seq_len, head_dim]
+ * tensor followed by dropout.  NOTE the argument order (seq_len, head_dim,
+ * num_heads) and that `head_dim` is the softmax axis: for attention
+ * probabilities [B,H,S,S] pass seq_len = S, head_dim = S.
+ * reference src/kernels/fused_softmax_dropout.cu:324-342 */
+TensorFuseStatus fused_softmax_dropout_fp16_wrapper(const void* input, void* output,
+                                                    unsigned char* dropout_mask, int batch_size,
+                                                    int seq_len, int head_dim, int num_heads,
+                                                    float dropout_prob, unsigned long long seed,
+                                                    cudaStream_t stream);
+TensorFuseStatus fused_softmax_dropout_fp32_wrapper(const void* input, void* output,
+                                                    unsigned char* dropout_mask, int batch_size,
+                                                    int seq_len, int head_dim, int num_heads,
+                                                    float dropout_prob, unsigned long long seed,
+                                                    cudaStream_t stream);
+
+/* ------------------------------------------------------------------ part 2
+ * Additions of this build; no reference declaration unless stated. */
+
+/* General INT8 entry: in-kernel dequantisation with selectable bias / output
+ * type and convention.
+ *   epilogue 1: out = gelu(fma(float(acc), scale_A*scale_B, bias)), out FLOAT16 or FLOAT32
+ *   epilogue 2: the reference convention above, bias FLOAT32, out FLOAT32
+ *   epilogue 3: out = acc (INT32), bias unused
+ * bias_dtype / out_dtype are TensorFuseDataType values. */
+TensorFuseStatus tensorfuse_b200_gemm_int8(const void* A, const void* B, const void* bias, void* C,
+                                           int M, int N, int K, float scale_A, float scale_B,
+                                           int bias_dtype, int out_dtype, int epilogue,
+                                           cudaStream_t stream);
+
+/* Row-sharded softmax+dropout: `rows` rows of length `row_len`; `first_row`
+ * is the index of the first of them inside the whole tensor, so that a shard
+ * draws exactly the dropout decisions it would get as part of the whole.
+ * dtype is TENSORFUSE_FLOAT16 or TENSORFUSE_FLOAT32. */
+TensorFuseStatus tensorfuse_b200_softmax_dropout_rows(const void* input, void* output,
+                                                      unsigned char* dropout_mask, long long rows,
+                                                      int row_len, int dtype, float dropout_prob,
+                                                      unsigned long long seed,
+                                                      unsigned long long first_row,
+                                                      cudaStream_t stream);
+
+/* The summation schedule the softmax kernel uses for a row of `row_len`
+ * elements (vec = elements per thread step, warps = warps per row); a CPU that
+ * follows the same schedule reproduces the result bit for bit. */
+void tensorfuse_b200_softmax_schedule(int row_len, int dtype, int aligned16, int* vec, int* warps);
+
+/* Seed source of tensorfuse_fused_softmax_dropout: after this call the n-th
+ * dropout call uses a seed derived from (seed, n).  Declared, but a no-op, in
+ * the reference (src/tensorfuse.h:60, src/python/core_bindings.cpp:840-843). */
+void tensorfuse_b200_set_random_seed(unsigned long long seed);
+/* The seed the most recent tensorfuse_fused_softmax_dropout call on this thread used. */
+unsigned long long tensorfuse_b200_last_softmax_seed(void);
+
+/* Host-buffer operators: the operands live in host memory (pinned memory is
+ * copied asynchronously, pageable memory works but is slower).  Rows are split
+ * over the devices chosen at tensorfuse_init; on every device the shard moves
+ * through a copy-in / compute / copy-out pipeline on three streams, weights are
+ * replicated.  Blocking.  These replace the staging the reference's Python
+ * binding performs (src/python/core_bindings.cpp:360-633 and 635-771:
+ * cudaMalloc, synchronous copies, one device).
+ * dtypes are TensorFuseDataType values; for INT8 operands `epilogue` is as for
+ * tensorfuse_b200_gemm_int8, otherwise it is ignored. */
+TensorFuseStatus tensorfuse_b200_gemm_bias_gelu_host(const void* A, const void* B, const void* bias,
+                                                     void* C, int M, int N, int K, int in_dtype,
+                                                     int bias_dtype, int out_dtype, int epilogue,
+                                                     float scale_A, float scale_B);
+TensorFuseStatus tensorfuse_b200_softmax_dropout_host(const void* input, void* output,
+                                                      unsigned char* dropout_mask, long long rows,
+                                                      int row_len, int dtype, float dropout_prob,
+                                                      unsigned long long seed);
+/* Page-locked host memory for the calls above. */
+void* tensorfuse_b200_alloc_pinned(size_t bytes);
+void tensorfuse_b200_free_pinned(void* p);
+
+/* The row split the host-buffer operators use: `parts` contiguous ranges whose
+ * starts are multiples of `align`; begins/counts receive `parts` entries. */
+void tensorfuse_b200_plan_shards(long long rows, int parts, int align, long long* begins,
+                                 long long* counts);
+
+/* Devices selected at init (count, and the ordinal of the i-th). */
+int tensorfuse_b200_device_count(void);
+int tensorfuse_b200_device_id(int i);
+
+/* Device-side watchdog: every wait inside the kernels is bounded; 0 = no wait
+ * has expired since the last reset, otherwise the code of the first one. */
+int tensorfuse_b200_watchdog_status(void);
+void tensorfuse_b200_watchdog_reset(void);
+
+/* Number of CUDA kernels this library has launched in this process. */
+unsigned long long tensorfuse_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TENSORFUSE_B200_H_ */

@@ -1,0 +1,216 @@
+"""Python face of the CPU oracle (TEST INFRASTRUCTURE ONLY).
+
+Only the test-suite, the smoke check and the CPU-baseline leg of the benchmark
+may import this module; the shipped package never does.
+
+Two families of functions:
+
+* thin ctypes wrappers over ``liboracle.so`` (built from ``oracle.c`` by
+  ``oracle/Makefile``) -- the scalar-loop restatement of the reference's C++
+  test oracles, plus the operation-by-operation "exact" softmax+dropout;
+* numpy twins restating the reference's numpy oracle
+  (``src/tests/python/test_mathematical_verification.py:29-58`` in the
+  reference project): ``np_gelu``, ``np_gemm_bias_gelu``, ``np_softmax``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+
+
+def build(force: bool = False) -> str:
+    """Compile liboracle.so if it is missing (or stale) and return its path."""
+    src = os.path.join(_HERE, "oracle.c")
+    stale = (not os.path.exists(_LIB_PATH)) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src)
+    if force or stale:
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB_PATH)
+        vp, i, l, f, u64 = C.c_void_p, C.c_int, C.c_long, C.c_float, C.c_uint64
+        L.tfo_max_threads.restype = i
+        L.tfo_gelu_f32.restype = f
+        L.tfo_gelu_f32.argtypes = [f]
+        L.tfo_gelu_f32_array.argtypes = [vp, vp, l]
+        L.tfo_gemm_bias_gelu_f32.argtypes = [vp, vp, vp, vp, i, i, i, f, f, i]
+        L.tfo_gemm_bias_gelu_f16.argtypes = [vp, vp, vp, vp, i, i, i, f, f, i]
+        L.tfo_gemm_i8_acc.argtypes = [vp, vp, vp, i, i, i, i]
+        L.tfo_i8_epilogue_f16.argtypes = [vp, vp, vp, l, i, f, f]
+        L.tfo_i8_epilogue_legacy_f32.argtypes = [vp, vp, vp, l, i, f, f]
+        L.tfo_softmax_ref_f32.argtypes = [vp, vp, l, i, i]
+        L.tfo_softmax_ref_f16.argtypes = [vp, vp, vp, l, i, i]
+        L.tfo_philox4x32_10.argtypes = [C.c_uint32] * 6 + [vp]
+        L.tfo_dropout_threshold.restype = C.c_uint32
+        L.tfo_dropout_threshold.argtypes = [f]
+        L.tfo_dropout_mask.argtypes = [vp, u64, l, f, u64]
+        L.tfo_softmax_dropout_exact.argtypes = [vp, vp, vp, l, i, i, f, u64, u64, i, i, i]
+        _lib = L
+    return _lib
+
+
+def _p(a: np.ndarray):
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def max_threads() -> int:
+    return int(lib().tfo_max_threads())
+
+
+# ----------------------------------------------------------------- C oracle
+
+def gelu(x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    y = np.empty_like(x)
+    lib().tfo_gelu_f32_array(_p(x), _p(y), x.size)
+    return y
+
+
+def gemm_bias_gelu_f32(A, B, bias, alpha=1.0, beta=1.0, threads=0):
+    A = np.ascontiguousarray(A, np.float32); B = np.ascontiguousarray(B, np.float32)
+    bias = np.ascontiguousarray(bias, np.float32)
+    M, K = A.shape; N = B.shape[1]
+    out = np.empty((M, N), np.float32)
+    lib().tfo_gemm_bias_gelu_f32(_p(A), _p(B), _p(bias), _p(out), M, N, K, alpha, beta, threads)
+    return out
+
+
+def gemm_bias_gelu_f16(A, B, bias, alpha=1.0, beta=1.0, threads=0):
+    A = np.ascontiguousarray(A, np.float16); B = np.ascontiguousarray(B, np.float16)
+    bias = np.ascontiguousarray(bias, np.float16)
+    M, K = A.shape; N = B.shape[1]
+    out = np.empty((M, N), np.float16)
+    lib().tfo_gemm_bias_gelu_f16(_p(A), _p(B), _p(bias), _p(out), M, N, K, alpha, beta, threads)
+    return out
+
+
+def gemm_i8_acc(A, B, threads=0):
+    A = np.ascontiguousarray(A, np.int8); B = np.ascontiguousarray(B, np.int8)
+    M, K = A.shape; N = B.shape[1]
+    acc = np.empty((M, N), np.int32)
+    lib().tfo_gemm_i8_acc(_p(A), _p(B), _p(acc), M, N, K, threads)
+    return acc
+
+
+def i8_epilogue_f16(acc, bias, scale_a, scale_b):
+    acc = np.ascontiguousarray(acc, np.int32); bias = np.ascontiguousarray(bias, np.float16)
+    out = np.empty(acc.shape, np.float16)
+    lib().tfo_i8_epilogue_f16(_p(acc), _p(bias), _p(out), acc.shape[0], acc.shape[1],
+                              scale_a, scale_b)
+    return out
+
+
+def i8_epilogue_legacy_f32(acc, bias, scale_a, scale_b):
+    acc = np.ascontiguousarray(acc, np.int32); bias = np.ascontiguousarray(bias, np.float32)
+    out = np.empty(acc.shape, np.float32)
+    lib().tfo_i8_epilogue_legacy_f32(_p(acc), _p(bias), _p(out), acc.shape[0], acc.shape[1],
+                                     scale_a, scale_b)
+    return out
+
+
+def softmax_ref_f32(x, threads=0):
+    x = np.ascontiguousarray(x, np.float32)
+    L = x.shape[-1]
+    out = np.empty_like(x)
+    lib().tfo_softmax_ref_f32(_p(x), _p(out), x.size // L, L, threads)
+    return out
+
+
+def softmax_ref_f16(x, threads=0):
+    x = np.ascontiguousarray(x, np.float16)
+    L = x.shape[-1]
+    out = np.empty_like(x)
+    mask = np.empty(x.shape, np.uint8)
+    lib().tfo_softmax_ref_f16(_p(x), _p(out), _p(mask), x.size // L, L, threads)
+    return out, mask
+
+
+def philox4x32_10(counter, key):
+    out = np.empty(4, np.uint32)
+    lib().tfo_philox4x32_10(*[int(c) for c in counter], int(key[0]), int(key[1]), _p(out))
+    return out
+
+
+def dropout_threshold(p) -> int:
+    return int(lib().tfo_dropout_threshold(float(p)))
+
+
+def dropout_mask(n, p, seed, first_idx=0):
+    m = np.empty(n, np.uint8)
+    lib().tfo_dropout_mask(_p(m), first_idx, n, p, seed)
+    return m
+
+
+def softmax_dropout_exact(x, p=0.0, seed=0, first_row=0, vec=8, warps=1, threads=0):
+    """Bit-reproducible softmax+dropout over the last axis.
+
+    ``vec``/``warps`` name the summation schedule (see oracle.c); the library
+    reports the schedule it uses for a given row length and dtype through
+    ``tensorfuse_b200_softmax_schedule``.
+    """
+    assert x.dtype in (np.float16, np.float32)
+    x = np.ascontiguousarray(x)
+    L = x.shape[-1]
+    out = np.empty_like(x)
+    mask = np.empty(x.shape, np.uint8)
+    lib().tfo_softmax_dropout_exact(_p(x), _p(out), _p(mask), x.size // L, L,
+                                    1 if x.dtype == np.float16 else 0, p, seed, first_row,
+                                    vec, warps, threads)
+    return out, mask
+
+
+# -------------------------------------------------------------- numpy twins
+
+def np_gelu(x):
+    a, b = 0.7978845608028654, 0.044715
+    return x * 0.5 * (1.0 + np.tanh(a * (x + b * x * x * x)))
+
+
+def np_gemm_bias_gelu(A, B, bias, alpha=1.0, beta=1.0):
+    return np_gelu(alpha * np.matmul(A, B) + beta * bias)
+
+
+def np_softmax(x, axis=-1):
+    z = x - np.max(x, axis=axis, keepdims=True)
+    e = np.exp(z)
+    return e / np.sum(e, axis=axis, keepdims=True)
+
+
+# --------------------------------------------------------------- comparisons
+
+def f16_ulp_distance(a, b):
+    """Distance in FP16 units-in-the-last-place between two float16 arrays
+    (monotone integer mapping of the bit patterns; +0 and -0 coincide)."""
+    def key(v):
+        u = np.ascontiguousarray(v, np.float16).view(np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u)
+    return np.abs(key(a) - key(b))
+
+
+def f16_parity_violations(got, want, max_ulp=1, tiny_abs=2.0 ** -22):
+    """Count elements of two float16 arrays that differ by more than ``max_ulp``
+    FP16 ulps.  Below the smallest normal FP16 (2^-14) the ulp is the fixed
+    subnormal step 2^-24 and the FP32 tanh form of GELU is itself only accurate
+    to a few of those steps (1 + tanh cancels), so there the bound is
+    ``tiny_abs`` absolute."""
+    g = np.asarray(got, np.float16); w = np.asarray(want, np.float16)
+    d = f16_ulp_distance(g, w)
+    small = np.abs(w.astype(np.float32)) < 2.0 ** -14
+    bad_normal = (~small) & (d > max_ulp)
+    bad_small = small & (np.abs(g.astype(np.float32) - w.astype(np.float32)) > tiny_abs)
+    return int(bad_normal.sum() + bad_small.sum())

@@ -1,0 +1,81 @@
+// kernels.h -- internal launcher interface between the C ABI layer and the
+// CUDA translation units.  Plain pointers and sizes only.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace tfb {
+
+// Storage types as seen by the launchers (values equal TensorFuseDataType).
+enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kI8 = 3, kU8 = 4, kI32 = 5 };
+
+// Result of a launcher; mapped 1:1 on TensorFuseStatus by the ABI layer.
+enum LaunchResult : int {
+  kOk = 0,
+  kInvalidArgument = 1,
+  kCudaError = 2,
+  kLaunchFailed = 6,
+  kUnsupported = 10,
+};
+
+// ------------------------------------------------------- softmax + dropout
+// Summation schedule the kernel uses for a row of L elements; the CPU oracle
+// takes the same two numbers to reproduce the result bit for bit.
+//   vec   : consecutive elements owned by one thread per step (8 or 1)
+//   warps : warps cooperating on one row (1 = warp-per-row kernel)
+struct SoftmaxSchedule {
+  int vec;
+  int warps;
+};
+SoftmaxSchedule softmax_schedule(int L, int dtype, bool aligned16);
+
+// rows x L, softmax over L, dropout with probability p, Philox stream keyed by
+// seed and indexed by (first_row + row) * L + col.
+LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* mask,
+                                    long long rows, int L, int dtype, float p,
+                                    unsigned long long seed, unsigned long long first_row,
+                                    cudaStream_t stream);
+
+// ------------------------------------------------------ GEMM + bias + GELU
+enum Epilogue : int {
+  kEpiGelu = 0,        // out = gelu(alpha*acc + beta*bias)                 (FP32 / FP16 paths)
+  kEpiI8Dequant = 1,   // out = gelu(fma(float(acc), scale, bias))          (INT8, multiply convention)
+  kEpiI8Legacy = 2,    // out = gelu_clamped(acc/scale + bias)*scale, non-finite -> 0 (INT8, reference convention)
+  kEpiI8Raw = 3,       // out = acc (INT32), no bias, no activation
+};
+
+struct GemmArgs {
+  const void* A;     // [M,K] row-major
+  const void* B;     // [K,N] row-major
+  const void* bias;  // [N]
+  void* C;           // [M,N] row-major
+  int M, N, K;
+  int in_dtype;      // kF32 | kF16 | kI8
+  int bias_dtype;    // kF32 | kF16
+  int out_dtype;     // kF32 | kF16 | kI32
+  int epilogue;
+  float alpha, beta, scale;       // scale: product of the host-known dequant factors
+  const float* scale_a_dev;       // optional device pointers to one float each; multiplied
+  const float* scale_b_dev;       // into `scale` on the device
+};
+
+// True when the tensor-core (TMA + tcgen05) kernel can take this problem:
+// FP16 or INT8 operands, 16-byte aligned base pointers and row pitches.
+bool gemm_tc_eligible(const GemmArgs& a);
+LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
+// Any shape, any alignment; CUDA-core FMA kernel with the same fused epilogue.
+LaunchResult launch_gemm_simt(const GemmArgs& a, cudaStream_t stream);
+// Picks the tensor-core kernel when eligible, else the CUDA-core kernel.
+LaunchResult launch_gemm(const GemmArgs& a, cudaStream_t stream);
+
+// Device-side watchdog: 0 when no bounded wait has expired since the last
+// reset, else the code of the first wait that gave up.
+int watchdog_status();
+void watchdog_reset();
+int* watchdog_word();  // host-mapped word the kernels write
+
+// Number of kernels this library has launched in the calling process.
+unsigned long long launch_count();
+void count_launch(int n = 1);
+
+}  // namespace tfb

@@ -1,0 +1,83 @@
+// runtime.h -- process-wide state of the library: the initialised flag, the
+// device list chosen at init, per-device streams / events / staging buffers for
+// the host-buffer operators, the dropout seed source and the watchdog word.
+//
+// Stands where the reference has src/runtime/runtime_context.{h,cpp} and
+// memory_manager.{h,cpp} (a single-device context with cuBLAS/cuDNN/cuRAND
+// handles and a first-fit pool that no operator ever calls): here the state is
+// what the two fused operators actually need, and the device list is honoured.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <vector>
+
+#include "tensorfuse/types.h"
+
+namespace tfb {
+
+// Grow-only device buffer.
+struct DevBuffer {
+  void* ptr = nullptr;
+  size_t cap = 0;
+  cudaError_t reserve(size_t bytes);
+  void release();
+};
+
+struct DeviceCtx {
+  int id = 0;
+  bool ready = false;
+  cudaStream_t s_in = nullptr, s_compute = nullptr, s_out = nullptr;
+  std::vector<cudaEvent_t> ev_in, ev_done;  // one pair per in-flight chunk
+  cudaEvent_t ev_weights = nullptr;
+  DevBuffer a, b, bias, c, mask;            // staging for the host-buffer operators
+  cudaError_t ensure(size_t chunks);
+  void destroy();
+};
+
+class Runtime {
+ public:
+  static Runtime& get();
+  TensorFuseStatus init(const TensorFuseConfig* cfg);
+  TensorFuseStatus shutdown();
+  bool initialized();
+  int log_level();
+  std::vector<int> devices();
+  DeviceCtx* ctx(size_t i);  // i-th selected device; contexts are created lazily
+
+  void set_seed(unsigned long long seed);
+  unsigned long long next_seed();
+
+ private:
+  std::mutex mu_;
+  bool initialized_ = false;
+  TensorFuseConfig cfg_{};
+  std::vector<int> devices_;
+  std::vector<DeviceCtx> ctxs_;
+  bool seeded_ = false;
+  unsigned long long seed_base_ = 0, seed_calls_ = 0;
+};
+
+// Sets the current device for the lifetime of the object when it differs.
+class DeviceGuard {
+ public:
+  explicit DeviceGuard(int dev);
+  ~DeviceGuard();
+ private:
+  int prev_ = -1;
+  bool switched_ = false;
+};
+
+// Device that owns a device pointer, or -1 when it cannot be told (host memory,
+// unregistered, error).
+int device_of_pointer(const void* p);
+// True when p is page-locked host memory known to the CUDA runtime.
+bool is_pinned_host(const void* p);
+
+// Contiguous, balanced split of `rows` rows into `parts` ranges whose starts are
+// multiples of `align` (the last range absorbs the remainder; empty ranges are
+// legal when rows < parts * align).
+void plan_shards(long long rows, int parts, int align, long long* begins, long long* counts);
+
+}  // namespace tfb

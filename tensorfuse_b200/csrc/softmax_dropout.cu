@@ -1,0 +1,461 @@
+// softmax_dropout.cu -- fused row softmax + dropout for sm_100a.
+//
+// Replaces the reference kernels fused_softmax_dropout_warp_kernel /
+// fused_softmax_dropout_kernel (reference src/kernels/fused_softmax_dropout.cu:39-233):
+//   m = max_j x_j;  e_j = exp(x_j - m);  y_j = e_j / sum_j e_j;
+//   keep_j = (p == 0) or (u_j > p);  out_j = keep_j ? y_j / (1-p) : 0;  mask_j = keep_j
+// with FP32 arithmetic on FP16 or FP32 storage.
+//
+// Memory-bound by construction (2 B read + 2 B write + 1 B mask per FP16
+// element), so the kernels are organised around 16-byte accesses and a row that
+// stays in registers between the reductions and the store:
+//   * warp-per-row kernel for rows up to 2048 elements: lane l owns the 8-element
+//     units l, l+32, ...; one 128-bit load per unit, shuffle reductions, one
+//     128-bit store plus one 64-bit mask store per unit; the next row's loads are
+//     issued before the current row is processed.
+//   * CTA-per-row kernel for longer or unaligned rows: three passes over a row
+//     that is L2-resident after the first.
+//
+// Arithmetic is written so that a CPU can reproduce every bit: the exponential
+// is a round-to-nearest range reduction plus a degree-5 FMA polynomial (no
+// MUFU), sums follow a fixed schedule (two accumulators per thread, xor
+// butterfly per warp, warps in ascending order), the reciprocal is IEEE.  The
+// packed fma/add/mul.f32x2 instructions of sm_100 keep the instruction count of
+// that polynomial close to a MUFU-based one.
+//
+// Dropout uses Philox4x32-10: eight consecutive elements share one block
+// (counter = global element index / 8, key = seed), each element takes a 16-bit
+// field and is kept when field >= round(p * 65536).  The counter depends only on
+// the element's position in the whole tensor, so any row-sharding across GPUs
+// reproduces the same mask.
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include "kernels.h"
+#include "ptx.cuh"
+
+namespace tfb {
+namespace {
+
+struct SmParams {
+  const void* in;
+  void* out;
+  unsigned char* mask;
+  long long rows;
+  int L;
+  float keep_scale;              // 1/(1-p), 0 when p >= 1
+  uint32_t thr;                  // drop when field < thr
+  unsigned long long first_row;  // row offset of this shard inside the whole tensor
+  uint32_t key[20];              // Philox round keys
+};
+
+constexpr float kLog2e = 0x1.715476p+0f;
+constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+constexpr float kC0 = 0x1.000002p+0f, kC1 = 0x1.62e428p-1f, kC2 = 0x1.ebf918p-3f,
+                kC3 = 0x1.c6b6e4p-5f, kC4 = 0x1.3d0c52p-7f, kC5 = 0x1.5c08e6p-10f;
+
+// 2^t for two values t in [-127, ~0] at once; t = -127 yields exactly 0.
+__device__ __forceinline__ uint64_t exp2_pair(uint64_t t2) {
+  const uint64_t magic2 = pack2(kMagic, kMagic);
+  const uint64_t r2 = add2(t2, magic2);
+  const uint64_t nf2 = sub2(r2, magic2);
+  const uint64_t f2 = sub2(t2, nf2);
+  uint64_t p2 = pack2(kC5, kC5);
+  p2 = fma2(p2, f2, pack2(kC4, kC4));
+  p2 = fma2(p2, f2, pack2(kC3, kC3));
+  p2 = fma2(p2, f2, pack2(kC2, kC2));
+  p2 = fma2(p2, f2, pack2(kC1, kC1));
+  p2 = fma2(p2, f2, pack2(kC0, kC0));
+  const float2 r = unpack2(r2);
+  const uint32_t s0 = (__float_as_uint(r.x) << 23) + 0x3f800000u;
+  const uint32_t s1 = (__float_as_uint(r.y) << 23) + 0x3f800000u;
+  return mul2(p2, pack2(__uint_as_float(s0), __uint_as_float(s1)));
+}
+
+// e = 2^(max(x*log2e - c, -127)) for a pair.
+__device__ __forceinline__ uint64_t exp_pair(float x0, float x1, uint64_t log2e2, uint64_t negc2) {
+  const float2 t = unpack2(fma2(pack2(x0, x1), log2e2, negc2));
+  return exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f)));
+}
+
+__device__ __forceinline__ void philox_block(uint32_t c0, uint32_t c1, const uint32_t* key,
+                                             uint32_t (&o)[4]) {
+  uint32_t c2 = 0u, c3 = 0u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ key[2 * r];
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ key[2 * r + 1];
+    c1 = (uint32_t)p1;
+    c3 = (uint32_t)p0;
+    c0 = n0;
+    c2 = n2;
+  }
+  o[0] = c0; o[1] = c1; o[2] = c2; o[3] = c3;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+__device__ __forceinline__ float warp_sum_butterfly(float v) {
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
+// ------------------------------------------------------------ 8-element units
+template <typename T> struct Unit;
+template <> struct Unit<__half> {
+  uint4 raw;
+  __device__ __forceinline__ void load(const __half* p) { raw = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  __device__ __forceinline__ void fill_neg_inf() { raw = make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u); }
+  __device__ __forceinline__ void widen(float (&x)[8]) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[k]));
+      x[2 * k] = f.x; x[2 * k + 1] = f.y;
+    }
+  }
+};
+template <> struct Unit<float> {
+  uint4 raw[2];
+  __device__ __forceinline__ void load(const float* p) {
+    raw[0] = __ldcs(reinterpret_cast<const uint4*>(p));
+    raw[1] = __ldcs(reinterpret_cast<const uint4*>(p) + 1);
+  }
+  __device__ __forceinline__ void fill_neg_inf() {
+    raw[0] = raw[1] = make_uint4(0xFF800000u, 0xFF800000u, 0xFF800000u, 0xFF800000u);
+  }
+  __device__ __forceinline__ void widen(float (&x)[8]) const {
+    x[0] = __uint_as_float(raw[0].x); x[1] = __uint_as_float(raw[0].y);
+    x[2] = __uint_as_float(raw[0].z); x[3] = __uint_as_float(raw[0].w);
+    x[4] = __uint_as_float(raw[1].x); x[5] = __uint_as_float(raw[1].y);
+    x[6] = __uint_as_float(raw[1].z); x[7] = __uint_as_float(raw[1].w);
+  }
+};
+
+// Scale, drop and store one unit.  e2[k] holds elements 2k, 2k+1.
+template <typename T, bool DROP>
+__device__ __forceinline__ void finish_unit(const uint64_t (&e2)[4], uint64_t g2, T* out,
+                                            unsigned char* mask, const SmParams& p,
+                                            unsigned long long philox_blk) {
+  uint32_t keep[4][2];  // keep[k][h]: element 2k+h survives
+  if (DROP) {
+    uint32_t o[4];
+    philox_block((uint32_t)philox_blk, (uint32_t)(philox_blk >> 32), p.key, o);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      keep[k][0] = (o[k] & 0xFFFFu) >= p.thr;
+      keep[k][1] = (o[k] >> 16) >= p.thr;
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) keep[k][0] = keep[k][1] = 1u;
+  }
+  uint2 mb;
+  mb.x = keep[0][0] | (keep[0][1] << 8) | (keep[1][0] << 16) | (keep[1][1] << 24);
+  mb.y = keep[2][0] | (keep[2][1] << 8) | (keep[3][0] << 16) | (keep[3][1] << 24);
+  __stcs(reinterpret_cast<uint2*>(mask), mb);
+
+  float2 y[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) y[k] = unpack2(mul2(e2[k], g2));
+  if constexpr (sizeof(T) == 2) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __half2 h = __floats2half2_rn(y[k].x, y[k].y);
+      uint32_t bits = *reinterpret_cast<const uint32_t*>(&h);
+      if (DROP) bits &= (keep[k][0] ? 0x0000FFFFu : 0u) | (keep[k][1] ? 0xFFFF0000u : 0u);
+      w[k] = bits;
+    }
+    __stcs(reinterpret_cast<uint4*>(out), make_uint4(w[0], w[1], w[2], w[3]));
+  } else {
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[2 * k] = (!DROP || keep[k][0]) ? y[k].x : 0.0f;
+      v[2 * k + 1] = (!DROP || keep[k][1]) ? y[k].y : 0.0f;
+    }
+    float4* o4 = reinterpret_cast<float4*>(out);
+    __stcs(o4, make_float4(v[0], v[1], v[2], v[3]));
+    __stcs(o4 + 1, make_float4(v[4], v[5], v[6], v[7]));
+  }
+}
+
+// ------------------------------------------------------- warp-per-row kernel
+// CH = units per lane (row length <= 256*CH).  8 warps per CTA, grid-stride
+// over rows, next row's loads in flight while the current row is processed.
+template <typename T, int CH, bool DROP>
+__global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
+  const int lane = threadIdx.x & 31;
+  const int L = p.L;
+  const long long stride = (long long)gridDim.x * 8;
+  long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const T* in = static_cast<const T*>(p.in);
+  T* out = static_cast<T*>(p.out);
+
+  bool valid[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) valid[c] = (lane + 32 * c) * 8 < L;
+
+  Unit<T> cur[CH], nxt[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    if (valid[c]) cur[c].load(in + row * L + (lane + 32 * c) * 8);
+    else cur[c].fill_neg_inf();
+  }
+
+  const uint64_t log2e2 = pack2(kLog2e, kLog2e);
+  for (; row < p.rows; row += stride) {
+    const long long next_row = row + stride;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      if (valid[c] && next_row < p.rows) nxt[c].load(in + next_row * L + (lane + 32 * c) * 8);
+      else nxt[c].fill_neg_inf();
+    }
+
+    float x[CH][8];
+    float m = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      cur[c].widen(x[c]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, x[c][i]);
+    }
+    m = warp_max(m);
+    if (m == -INFINITY) m = 0.0f;
+    const float negc = -__fmul_rn(m, kLog2e);
+    const uint64_t negc2 = pack2(negc, negc);
+
+    uint64_t e2[CH][4];
+    uint64_t s2 = pack2(0.0f, 0.0f);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        e2[c][k] = exp_pair(x[c][2 * k], x[c][2 * k + 1], log2e2, negc2);
+        s2 = add2(s2, e2[c][k]);
+      }
+    }
+    const float2 s = unpack2(s2);
+    const float total = warp_sum_butterfly(__fadd_rn(s.x, s.y));
+    const float inv = (total == 0.0f) ? 0.0f : __fdiv_rn(1.0f, total);
+    const float g = __fmul_rn(inv, p.keep_scale);
+    const uint64_t g2 = pack2(g, g);
+
+    const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)L) >> 3;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      if (valid[c]) {
+        const long long off = row * L + (lane + 32 * c) * 8;
+        finish_unit<T, DROP>(e2[c], g2, out + off, p.mask + off, p, blk0 + (unsigned)(lane + 32 * c));
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CH; ++c) cur[c] = nxt[c];
+  }
+}
+
+// -------------------------------------------------------- CTA-per-row kernel
+// Three passes over the row (the second and third are served by L2).  VEC = 8
+// needs 16-byte aligned rows and L % 8 == 0; VEC = 1 takes anything.
+template <typename T, int VEC, bool DROP>
+__global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
+  __shared__ float red[32];
+  const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = nthr >> 5;
+  const int L = p.L;
+  const int units = (L + VEC - 1) / VEC;
+  const T* in = static_cast<const T*>(p.in);
+  T* out = static_cast<T*>(p.out);
+  const uint64_t log2e2 = pack2(kLog2e, kLog2e);
+
+  for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T* xr = in + row * L;
+    // pass 1: maximum
+    float m = -INFINITY;
+    for (int u = tid; u < units; u += nthr) {
+      if constexpr (VEC == 8) {
+        Unit<T> un; un.load(xr + u * 8);
+        float x[8]; un.widen(x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
+      } else {
+        m = fmaxf(m, (float)xr[u]);
+      }
+    }
+    m = warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+    for (int w = 1; w < nwarps; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    if (m == -INFINITY) m = 0.0f;
+    const float negc = -__fmul_rn(m, kLog2e);
+    const uint64_t negc2 = pack2(negc, negc);
+
+    // pass 2: sum of exponentials
+    float lane_sum;
+    if constexpr (VEC == 8) {
+      uint64_t s2 = pack2(0.0f, 0.0f);
+      for (int u = tid; u < units; u += nthr) {
+        Unit<T> un; un.load(xr + u * 8);
+        float x[8]; un.widen(x);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s2 = add2(s2, exp_pair(x[2 * k], x[2 * k + 1], log2e2, negc2));
+      }
+      const float2 s = unpack2(s2);
+      lane_sum = __fadd_rn(s.x, s.y);
+    } else {
+      float s0 = 0.0f;
+      for (int u = tid; u < units; u += nthr) {
+        const float xv = (float)xr[u];
+        s0 = __fadd_rn(s0, unpack2(exp_pair(xv, xv, log2e2, negc2)).x);
+      }
+      lane_sum = __fadd_rn(s0, 0.0f);
+    }
+    lane_sum = warp_sum_butterfly(lane_sum);
+    if (lane == 0) red[warp] = lane_sum;
+    __syncthreads();
+    float total = red[0];
+    for (int w = 1; w < nwarps; ++w) total = __fadd_rn(total, red[w]);
+    __syncthreads();
+    const float inv = (total == 0.0f) ? 0.0f : __fdiv_rn(1.0f, total);
+    const float g = __fmul_rn(inv, p.keep_scale);
+    const uint64_t g2 = pack2(g, g);
+
+    // pass 3: normalise, drop, store
+    const unsigned long long idx0 = (p.first_row + (unsigned long long)row) * (unsigned long long)L;
+    for (int u = tid; u < units; u += nthr) {
+      if constexpr (VEC == 8) {
+        Unit<T> un; un.load(xr + u * 8);
+        float x[8]; un.widen(x);
+        uint64_t e2[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) e2[k] = exp_pair(x[2 * k], x[2 * k + 1], log2e2, negc2);
+        const long long off = row * L + (long long)u * 8;
+        finish_unit<T, DROP>(e2, g2, out + off, p.mask + off, p, (idx0 >> 3) + (unsigned)u);
+      } else {
+        const float xv = (float)xr[u];
+        const float e = unpack2(exp_pair(xv, xv, log2e2, negc2)).x;
+        float y = __fmul_rn(e, g);
+        unsigned keep = 1u;
+        if (DROP) {
+          const unsigned long long idx = idx0 + (unsigned)u;
+          uint32_t o[4];
+          philox_block((uint32_t)(idx >> 3), (uint32_t)(idx >> 35), p.key, o);
+          const uint32_t el = (uint32_t)(idx & 7ull);
+          const uint32_t word = (el >> 1) == 0 ? o[0] : (el >> 1) == 1 ? o[1] : (el >> 1) == 2 ? o[2] : o[3];
+          keep = ((word >> (16u * (el & 1u))) & 0xFFFFu) >= p.thr;
+          if (!keep) y = 0.0f;
+        }
+        p.mask[row * L + u] = (unsigned char)keep;
+        if constexpr (sizeof(T) == 2) out[row * L + u] = __float2half_rn(y);
+        else out[row * L + u] = y;
+      }
+    }
+  }
+}
+
+template <typename T, int CH>
+void launch_warp(const SmParams& p, bool drop, int sms, cudaStream_t stream) {
+  const long long ctas_needed = (p.rows + 7) / 8;
+  int per_sm = 0;
+  if (drop) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, softmax_warp_kernel<T, CH, true>, 256, 0);
+  else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, softmax_warp_kernel<T, CH, false>, 256, 0);
+  if (per_sm < 1) per_sm = 1;
+  const long long cap = (long long)sms * per_sm;
+  const int grid = (int)(ctas_needed < cap ? ctas_needed : cap);
+  if (drop) softmax_warp_kernel<T, CH, true><<<grid, 256, 0, stream>>>(p);
+  else softmax_warp_kernel<T, CH, false><<<grid, 256, 0, stream>>>(p);
+}
+
+template <typename T, int VEC>
+void launch_block(const SmParams& p, bool drop, int warps, int sms, cudaStream_t stream) {
+  const long long cap = (long long)sms * (warps == 1 ? 32 : 8);
+  const int grid = (int)(p.rows < cap ? p.rows : cap);
+  if (drop) softmax_block_kernel<T, VEC, true><<<grid, 32 * warps, 0, stream>>>(p);
+  else softmax_block_kernel<T, VEC, false><<<grid, 32 * warps, 0, stream>>>(p);
+}
+
+template <typename T>
+void dispatch(const SmParams& p, bool drop, SoftmaxSchedule sch, int sms, cudaStream_t stream) {
+  if (sch.vec == 8 && sch.warps == 1) {
+    if (p.L <= 256) launch_warp<T, 1>(p, drop, sms, stream);
+    else if (p.L <= 512) launch_warp<T, 2>(p, drop, sms, stream);
+    else if (p.L <= 1024) launch_warp<T, 4>(p, drop, sms, stream);
+    else launch_warp<T, 8>(p, drop, sms, stream);
+  } else if (sch.vec == 8) {
+    launch_block<T, 8>(p, drop, sch.warps, sms, stream);
+  } else {
+    launch_block<T, 1>(p, drop, sch.warps, sms, stream);
+  }
+}
+
+int sm_count_of_current_device() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (cached[dev] == 0) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = n > 0 ? n : 148;
+  }
+  return cached[dev];
+}
+
+}  // namespace
+
+SoftmaxSchedule softmax_schedule(int L, int dtype, bool aligned16) {
+  (void)dtype;
+  SoftmaxSchedule s;
+  if (aligned16 && L % 8 == 0) {
+    s.vec = 8;
+    s.warps = L <= 2048 ? 1 : 8;
+  } else {
+    s.vec = 1;
+    s.warps = L <= 1024 ? 1 : 8;
+  }
+  return s;
+}
+
+LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* mask,
+                                    long long rows, int L, int dtype, float p,
+                                    unsigned long long seed, unsigned long long first_row,
+                                    cudaStream_t stream) {
+  if (!in || !out || !mask) return kInvalidArgument;
+  if (!(p >= 0.0f && p <= 1.0f)) return kInvalidArgument;
+  if (dtype != kF16 && dtype != kF32) return kUnsupported;
+  if (rows < 0 || L < 0) return kInvalidArgument;
+  if (rows == 0 || L == 0) return kOk;
+
+  SmParams sp;
+  sp.in = in; sp.out = out; sp.mask = mask; sp.rows = rows; sp.L = L;
+  sp.keep_scale = p >= 1.0f ? 0.0f : 1.0f / (1.0f - p);
+  double t = floor((double)p * 65536.0 + 0.5);
+  sp.thr = p > 0.0f ? (uint32_t)(t > 65536.0 ? 65536.0 : t) : 0u;
+  sp.first_row = first_row;
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    sp.key[2 * r] = k0; sp.key[2 * r + 1] = k1;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  const bool drop = sp.thr != 0u;
+  const uintptr_t bits = (uintptr_t)in | (uintptr_t)out | ((uintptr_t)mask << 1);
+  const bool aligned16 = (bits & 15u) == 0;
+  const SoftmaxSchedule sch = softmax_schedule(L, dtype, aligned16);
+  const int sms = sm_count_of_current_device();
+  if (dtype == kF16) dispatch<__half>(sp, drop, sch, sms, stream);
+  else dispatch<float>(sp, drop, sch, sms, stream);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
+}
+
+}  // namespace tfb
