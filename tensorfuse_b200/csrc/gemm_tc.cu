@@ -312,22 +312,24 @@ struct MapKey {
   }
 };
 // Small per-thread cache: encoding a tensor map costs a few microseconds and the
-// same weight / activation buffers come back call after call.
-const CUtensorMap* cached_map(const MapKey& k) {
+// same weight / activation buffers come back call after call.  The map is
+// copied out, so a later insertion that recycles the slot cannot change it.
+bool cached_map(const MapKey& k, CUtensorMap* out) {
   constexpr int kSlots = 16;
   thread_local MapKey keys[kSlots];
   thread_local CUtensorMap maps[kSlots];
   thread_local bool used[kSlots] = {};
   thread_local int next = 0;
   for (int i = 0; i < kSlots; ++i)
-    if (used[i] && keys[i] == k) return &maps[i];
+    if (used[i] && keys[i] == k) { *out = maps[i]; return true; }
   const int slot = next;
   next = (next + 1) % kSlots;
   used[slot] = false;
-  if (!make_map(&maps[slot], k.base, k.es, k.rows, k.cols, k.box_rows)) return nullptr;
+  if (!make_map(&maps[slot], k.base, k.es, k.rows, k.cols, k.box_rows)) return false;
   keys[slot] = k;
   used[slot] = true;
-  return &maps[slot];
+  *out = maps[slot];
+  return true;
 }
 
 int sm_count() {
@@ -361,14 +363,15 @@ LaunchResult run(const GemmArgs& a, cudaStream_t stream) {
       attr_set[dev] = true;
     }
   }
-  const CUtensorMap* ma = cached_map(MapKey{a.A, ES, a.M, a.K, TBM});
-  const CUtensorMap* mb = cached_map(MapKey{a.B, ES, a.K, a.N, 128 / ES});
-  if (!ma || !mb) return kLaunchFailed;
+  CUtensorMap ma, mb;
+  if (!cached_map(MapKey{a.A, ES, a.M, a.K, TBM}, &ma) ||
+      !cached_map(MapKey{a.B, ES, a.K, a.N, 128 / ES}, &mb))
+    return kLaunchFailed;
   const int tiles = ((a.M + TBM - 1) / TBM) * ((a.N + TBN - 1) / TBN);
   const int sms = sm_count();
   const int grid = tiles < sms ? tiles : sms;
   EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev};
-  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(*ma, *mb, a.bias, a.bias_dtype,
+  kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, a.bias, a.bias_dtype,
                                                     static_cast<TOut*>(a.C), a.M, a.N, a.K, ep,
                                                     watchdog_word());
   count_launch();
