@@ -362,8 +362,57 @@ def side_workloads(tf, L, dev, peaks, args):
     return out
 
 
+def run_only(args):
+    """One kernel, device-resident operands, a handful of launches: the command
+    profiler captures are taken from (`--only gemm_fp16|gemm_int8|softmax|softmax_p0`)."""
+    import torch
+    import tensorfuse_b200 as tf
+    from tensorfuse_b200._lib import lib as L
+    torch.cuda.set_device(0)
+    tf.init()
+    dev = torch.device("cuda", 0)
+    sp = int(torch.cuda.current_stream().cuda_stream)
+    if args.only == "gemm_fp16":
+        A = torch.randn((M, K), device=dev).half(); B = (torch.randn((K, N), device=dev) / 32).half()
+        b = (torch.randn(N, device=dev) * 0.02).half(); C = torch.empty((M, N), dtype=torch.float16, device=dev)
+        fn = lambda: L.fused_gemm_bias_gelu_fp16_wrapper(A.data_ptr(), B.data_ptr(), b.data_ptr(), C.data_ptr(),
+                                                         M, N, K, 1.0, 1.0, sp)
+        work, unit = FLOP_PER_STEP / 1e12, "TFLOPS"
+    elif args.only == "gemm_int8":
+        Mi, Ki, Ni = 8192, 4096, 16384
+        A = torch.randint(-127, 128, (Mi, Ki), dtype=torch.int8, device=dev)
+        B = torch.randint(-127, 128, (Ki, Ni), dtype=torch.int8, device=dev)
+        b = (torch.randn(Ni, device=dev) * 0.02).half(); C = torch.empty((Mi, Ni), dtype=torch.float16, device=dev)
+        fn = lambda: L.tensorfuse_b200_gemm_int8(A.data_ptr(), B.data_ptr(), b.data_ptr(), C.data_ptr(), Mi, Ni, Ki,
+                                                 1e-2, 1e-4, 1, 1, 1, sp)
+        work, unit = 2.0 * Mi * Ni * Ki / 1e12, "TOPS"
+    else:
+        rows, Lr = 32 * 16 * 512, 512
+        x = (torch.randn((rows, Lr), device=dev) / 8).half(); o = torch.empty_like(x)
+        m = torch.empty((rows, Lr), dtype=torch.uint8, device=dev)
+        p = 0.0 if args.only == "softmax_p0" else 0.1
+        fn = lambda: L.tensorfuse_b200_softmax_dropout_rows(x.data_ptr(), o.data_ptr(), m.data_ptr(), rows, Lr, 1,
+                                                            p, 3, 0, sp)
+        work, unit = rows * Lr * 5 / 1e9, "GB/s"
+    for _ in range(max(1, args.warmup)):
+        assert fn() == 0
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        assert fn() == 0
+    e1.record(); torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    rate = work / (ms * 1e-3)
+    print(json.dumps({"only": args.only, "ms_per_launch": ms, "rate": rate, "unit": unit,
+                      "launches": args.steps + max(1, args.warmup), "watchdog": tf.watchdog_status()}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default=None, choices=["gemm_fp16", "gemm_int8", "softmax", "softmax_p0"],
+                    help="run a single kernel a few times (profiling aid)")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
@@ -371,6 +420,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.only:
+        return run_only(args)
     return run_gpu(args)
 
 

@@ -11,7 +11,9 @@ import ctypes as C
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "lib", "libtensorfuse.so")
+# TENSORFUSE_B200_LIB selects another build of the same library (e.g. one
+# compiled with different tuning constants); it is never a different backend.
+LIB_PATH = os.environ.get("TENSORFUSE_B200_LIB") or os.path.join(_PKG, "lib", "libtensorfuse.so")
 
 MAX_DIMS = 8
 

@@ -23,7 +23,7 @@ LIB = os.path.join(LIBDIR, "libtensorfuse.so")
 
 SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "runtime.cpp", "c_api.cpp",
            "host_ops.cpp"]
-HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h"]
+HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=default", "-DTENSORFUSE_WITH_CUDA_RUNTIME",
