@@ -231,12 +231,12 @@ void tfo_philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint3
 /* Dropout decision for the element with global flat index idx: eight
  * consecutive elements share one Philox block (counter = idx/8, key = seed);
  * element e = idx%8 takes the 16-bit field e%2 of word e/2 and is kept when
- * that field is >= thr, thr = round(p * 65536). */
+ * the low 15 bits of that field are >= thr, thr = round(p * 32768). */
 uint32_t tfo_dropout_threshold(float p) {
   if (!(p > 0.0f)) return 0u;
-  if (p >= 1.0f) return 65536u;
-  double t = floor((double)p * 65536.0 + 0.5);
-  if (t > 65536.0) t = 65536.0;
+  if (p >= 1.0f) return 32768u;
+  double t = floor((double)p * 32768.0 + 0.5);
+  if (t > 32768.0) t = 32768.0;
   return (uint32_t)t;
 }
 
@@ -246,7 +246,7 @@ static inline int dropout_keep(uint64_t idx, uint64_t seed, uint32_t thr) {
   tfo_philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u, (uint32_t)seed,
                     (uint32_t)(seed >> 32), o);
   uint32_t e = (uint32_t)(idx & 7u);
-  uint32_t field = (o[e >> 1] >> (16u * (e & 1u))) & 0xFFFFu;
+  uint32_t field = (o[e >> 1] >> (16u * (e & 1u))) & 0x7FFFu;
   return field >= thr;
 }
 
@@ -279,7 +279,29 @@ static inline float exp2_poly(float t) {
   return p * s;
 }
 
-/* One row.  x: L inputs already widened to FP32.  The summation order is the
+/* FP16-storage form of the exponential: the input is clamped from below at
+ * lo (about max - 64) before the multiply, so t stays within about [-116, 0]
+ * and 2^n is added straight into the exponent field; degree-4 polynomial. */
+static inline float exp2_poly_h(float t) {
+  const float MAGIC = 12582912.0f;
+  const float d0 = 0x1.ffffe8p-1f, d1 = 0x1.62e0dcp-1f, d2 = 0x1.ec06dap-3f,
+              d3 = 0x1.ca144p-5f, d4 = 0x1.3997d6p-7f;
+  float r = t + MAGIC;
+  float nf = r - MAGIC;
+  float f = t - nf;
+  float p = d4;
+  p = fmaf(p, f, d3);
+  p = fmaf(p, f, d2);
+  p = fmaf(p, f, d1);
+  p = fmaf(p, f, d0);
+  uint32_t rb, pb; memcpy(&rb, &r, 4); memcpy(&pb, &p, 4);
+  uint32_t eb = pb + (rb << 23);
+  float e; memcpy(&e, &eb, 4);
+  return e;
+}
+
+/* One row.  x: L inputs already widened to FP32.  half_form selects the
+ * FP16-storage exponential above (inputs are FP16 values), else the FP32 one.  The summation order is the
  * one a team of `warps` warps uses when unit u (V consecutive elements, V = vec)
  * belongs to thread u % (32*warps): every thread adds its elements in ascending
  * order into two accumulators (even / odd position inside the unit), adds the
@@ -287,12 +309,14 @@ static inline float exp2_poly(float t) {
  * warp totals are added in ascending warp order.  y receives e_j * g with
  * g = (1/sum) * keep_scale; an all -inf row gives zeros. */
 static void softmax_row_exact(const float* x, float* y, int L, int vec, int warps,
-                              float keep_scale) {
+                              float keep_scale, int half_form) {
   const float LOG2E = 0x1.715476p+0f;
   float mx = -INFINITY;
   for (int j = 0; j < L; ++j) mx = fmaxf(mx, x[j]);
-  if (mx == -INFINITY) mx = 0.0f;
+  const int all_masked = mx == -INFINITY;
+  if (all_masked) mx = 0.0f;
   const float c = mx * LOG2E;
+  const float lo = h2f(f2h(mx - 64.0f));
   const int T = 32 * warps;
   const int units = (L + vec - 1) / vec;
   float lane_sum[32 * 32];
@@ -302,8 +326,8 @@ static void softmax_row_exact(const float* x, float* y, int L, int vec, int warp
       for (int i = 0; i < vec; ++i) {
         int j = u * vec + i;
         if (j >= L) break;
-        float tt = fmaxf(fmaf(x[j], LOG2E, -c), -127.0f);
-        float e = exp2_poly(tt);
+        float e = half_form ? exp2_poly_h(fmaf(fmaxf(x[j], lo), LOG2E, -c))
+                            : exp2_poly(fmaxf(fmaf(x[j], LOG2E, -c), -127.0f));
         y[j] = e;
         if (i & 1) s1 += e; else s0 += e;
       }
@@ -321,7 +345,7 @@ static void softmax_row_exact(const float* x, float* y, int L, int vec, int warp
     }
     total = (w == 0) ? v[0] : total + v[0];
   }
-  const float inv = (total == 0.0f) ? 0.0f : 1.0f / total;
+  const float inv = (total == 0.0f || all_masked) ? 0.0f : 1.0f / total;
   const float g = inv * keep_scale;
   for (int j = 0; j < L; ++j) y[j] = y[j] * g;
 }
@@ -349,7 +373,7 @@ void tfo_softmax_dropout_exact(const void* in, void* out, uint8_t* mask, long ro
       } else {
         memcpy(x, (const float*)in + r * L, sizeof(float) * (size_t)L);
       }
-      softmax_row_exact(x, y, L, vec, warps, ks);
+      softmax_row_exact(x, y, L, vec, warps, ks, dtype == 1);
       for (int j = 0; j < L; ++j) {
         uint64_t idx = (first_row + (uint64_t)r) * (uint64_t)L + (uint64_t)j;
         int keep = thr == 0 ? 1 : dropout_keep(idx, seed, thr);

@@ -129,6 +129,9 @@ __device__ __forceinline__ float2 epilogue_pair(uint32_t r0, uint32_t r1, float 
     uint64_t x2;
     if constexpr (EPI == kEpiGelu) x2 = fma2(pack2(a0, a1), pack2(ep.alpha, ep.alpha), pack2(ep.beta * b0, ep.beta * b1));
     else x2 = fma2(pack2(a0, a1), pack2(ep.scale, ep.scale), pack2(b0, b1));
+#ifdef TFB_EXP_NO_GELU
+    return unpack2(x2);
+#endif
     const float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
     const float k2 = k1 * 0.044715f;
     const uint64_t w2 = fma2(mul2(x2, x2), pack2(k2, k2), pack2(k1, k1));
@@ -333,7 +336,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         uint32_t w[32];
         epilogue_chunk<EPI, TOut, kIntAcc>(acc[c & 1], bsh + c * 32, ep, w);
         if (c % CHUNKS_PER_BOX == 0) {
+#ifndef TFB_EXP_NO_WAIT
           if (lane == 0) bulk_wait_read_all();   // the previous box has left the staging buffer
+#endif
           __syncwarp();
         }
 #pragma unroll
@@ -344,7 +349,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           fence_async_smem();
           __syncwarp();
           const int x = nc + (c / CHUNKS_PER_BOX) * (128 / (int)sizeof(TOut));
+#ifdef TFB_EXP_NO_STORE
+          if (lane == 0 && x < N && row0 < M && N < 0) {
+#else
           if (lane == 0 && x < N && row0 < M) {
+#endif
             tma_store_2d(&tmC, staging, x, row0);
             bulk_commit();
           }

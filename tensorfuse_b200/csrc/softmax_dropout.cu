@@ -25,7 +25,7 @@
 //
 // Dropout uses Philox4x32-10: eight consecutive elements share one block
 // (counter = global element index / 8, key = seed), each element takes a 16-bit
-// field and is kept when field >= round(p * 65536).  The counter depends only on
+// field and is kept when its low 15 bits are >= round(p * 32768).  The counter depends only on
 // the element's position in the whole tensor, so any row-sharding across GPUs
 // reproduces the same mask.
 #include <cuda_fp16.h>
@@ -44,7 +44,9 @@ struct SmParams {
   long long rows;
   int L;
   float keep_scale;              // 1/(1-p), 0 when p >= 1
-  uint32_t thr;                  // drop when field < thr
+  uint32_t thr;                  // drop when the 15-bit field < thr (thr = round(p * 32768))
+  uint32_t thr_h2;               // thr in both halves of a word, for the packed FP16 compare
+  int hcmp;                      // thr <= 0x7C00: 15-bit fields order like positive FP16 numbers
   unsigned long long first_row;  // row offset of this shard inside the whole tensor
   uint32_t key[20];              // Philox round keys
 };
@@ -72,10 +74,55 @@ __device__ __forceinline__ uint64_t exp2_pair(uint64_t t2) {
   return mul2(p2, pack2(__uint_as_float(s0), __uint_as_float(s1)));
 }
 
-// e = 2^(max(x*log2e - c, -127)) for a pair.
-__device__ __forceinline__ uint64_t exp_pair(float x0, float x1, uint64_t log2e2, uint64_t negc2) {
-  const float2 t = unpack2(fma2(pack2(x0, x1), log2e2, negc2));
-  return exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f)));
+// FP16-storage form: the inputs have been clamped from below at lo ~ max - 64,
+// so t lies in about [-116, 0] and 2^n can be added into the exponent field
+// directly; degree-4 polynomial (max relative error 2.7e-6, two orders below an
+// FP16 ulp).
+constexpr float kD0 = 0x1.ffffe8p-1f, kD1 = 0x1.62e0dcp-1f, kD2 = 0x1.ec06dap-3f,
+                kD3 = 0x1.ca144p-5f, kD4 = 0x1.3997d6p-7f;
+__device__ __forceinline__ uint64_t exp2_pair_h(uint64_t t2) {
+  const uint64_t magic2 = pack2(kMagic, kMagic);
+  const uint64_t r2 = add2(t2, magic2);
+  const uint64_t nf2 = sub2(r2, magic2);
+  const uint64_t f2 = sub2(t2, nf2);
+  uint64_t p2 = pack2(kD4, kD4);
+  p2 = fma2(p2, f2, pack2(kD3, kD3));
+  p2 = fma2(p2, f2, pack2(kD2, kD2));
+  p2 = fma2(p2, f2, pack2(kD1, kD1));
+  p2 = fma2(p2, f2, pack2(kD0, kD0));
+  const float2 r = unpack2(r2), p = unpack2(p2);
+  const uint32_t e0 = __float_as_uint(p.x) + (__float_as_uint(r.x) << 23);
+  const uint32_t e1 = __float_as_uint(p.y) + (__float_as_uint(r.y) << 23);
+  return pack2(__uint_as_float(e0), __uint_as_float(e1));
+}
+
+// Row constants of the exponential.  lo is only used by the FP16-storage form.
+struct ExpCtx {
+  uint64_t log2e2, negc2;
+  float lo;
+};
+// m: row maximum (already 0 for an all -inf row).
+template <bool HF>
+__device__ __forceinline__ ExpCtx make_exp_ctx(float m) {
+  ExpCtx c;
+  const float negc = -__fmul_rn(m, kLog2e);
+  c.log2e2 = pack2(kLog2e, kLog2e);
+  c.negc2 = pack2(negc, negc);
+  c.lo = HF ? __half2float(__float2half_rn(__fsub_rn(m, 64.0f))) : 0.0f;
+  return c;
+}
+// FP32 storage: e = 2^(max(x*log2e - c, -127)).
+// FP16 storage: e = 2^(max(x, lo)*log2e - c); PRECLAMPED says the caller has
+// already applied the max on the packed halves.
+template <bool HF, bool PRECLAMPED = false>
+__device__ __forceinline__ uint64_t exp_pair(float x0, float x1, const ExpCtx& c) {
+  if constexpr (HF) {
+    if constexpr (!PRECLAMPED) { x0 = fmaxf(x0, c.lo); x1 = fmaxf(x1, c.lo); }
+    return exp2_pair_h(fma2(pack2(x0, x1), c.log2e2, c.negc2));
+  } else {
+    const float2 t = unpack2(fma2(pack2(x0, x1), c.log2e2, c.negc2));
+    return exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f)));
+  }
 }
 
 __device__ __forceinline__ void philox_block(uint32_t c0, uint32_t c1, const uint32_t* key,
@@ -138,27 +185,45 @@ template <> struct Unit<float> {
   }
 };
 
+// Keep decisions of one Philox block as four mask words: the low / high half of
+// km[k] is 0xFFFF when element 2k / 2k+1 survives.  A decision compares the low
+// 15 bits of a 16-bit field with thr; when thr <= 0x7C00 those 15-bit patterns
+// order exactly like non-negative FP16 numbers (patterns above 0x7C00 are NaNs,
+// for which "greater-or-unordered" is true, as it must be), so one packed FP16
+// compare decides two elements.
+template <bool DROP>
+__device__ __forceinline__ void keep_masks(const SmParams& p, unsigned long long philox_blk, uint32_t (&km)[4]) {
+  if (DROP) {
+    uint32_t o[4];
+    philox_block((uint32_t)philox_blk, (uint32_t)(philox_blk >> 32), p.key, o);
+    if (p.hcmp) {
+      const __half2 thr2 = *reinterpret_cast<const __half2*>(&p.thr_h2);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t f = o[k] & 0x7FFF7FFFu;
+        km[k] = __hgeu2_mask(*reinterpret_cast<const __half2*>(&f), thr2);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        km[k] = ((o[k] & 0x7FFFu) >= p.thr ? 0x0000FFFFu : 0u) | (((o[k] >> 16) & 0x7FFFu) >= p.thr ? 0xFFFF0000u : 0u);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) km[k] = 0xFFFFFFFFu;
+  }
+}
+
 // Scale, drop and store one unit.  e2[k] holds elements 2k, 2k+1.
 template <typename T, bool DROP>
 __device__ __forceinline__ void finish_unit(const uint64_t (&e2)[4], uint64_t g2, T* out,
                                             unsigned char* mask, const SmParams& p,
                                             unsigned long long philox_blk) {
-  uint32_t keep[4][2];  // keep[k][h]: element 2k+h survives
-  if (DROP) {
-    uint32_t o[4];
-    philox_block((uint32_t)philox_blk, (uint32_t)(philox_blk >> 32), p.key, o);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      keep[k][0] = (o[k] & 0xFFFFu) >= p.thr;
-      keep[k][1] = (o[k] >> 16) >= p.thr;
-    }
-  } else {
-#pragma unroll
-    for (int k = 0; k < 4; ++k) keep[k][0] = keep[k][1] = 1u;
-  }
-  uint2 mb;
-  mb.x = keep[0][0] | (keep[0][1] << 8) | (keep[1][0] << 16) | (keep[1][1] << 24);
-  mb.y = keep[2][0] | (keep[2][1] << 8) | (keep[3][0] << 16) | (keep[3][1] << 24);
+  uint32_t km[4];
+  keep_masks<DROP>(p, philox_blk, km);
+  uint2 mb;   // one byte per element: byte 0 / 2 of each mask word, reduced to 0 / 1
+  mb.x = __byte_perm(km[0], km[1], 0x6420) & 0x01010101u;
+  mb.y = __byte_perm(km[2], km[3], 0x6420) & 0x01010101u;
   __stcs(reinterpret_cast<uint2*>(mask), mb);
 
   float2 y[4];
@@ -169,17 +234,15 @@ __device__ __forceinline__ void finish_unit(const uint64_t (&e2)[4], uint64_t g2
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const __half2 h = __floats2half2_rn(y[k].x, y[k].y);
-      uint32_t bits = *reinterpret_cast<const uint32_t*>(&h);
-      if (DROP) bits &= (keep[k][0] ? 0x0000FFFFu : 0u) | (keep[k][1] ? 0xFFFF0000u : 0u);
-      w[k] = bits;
+      w[k] = *reinterpret_cast<const uint32_t*>(&h) & km[k];
     }
     __stcs(reinterpret_cast<uint4*>(out), make_uint4(w[0], w[1], w[2], w[3]));
   } else {
     float v[8];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      v[2 * k] = (!DROP || keep[k][0]) ? y[k].x : 0.0f;
-      v[2 * k + 1] = (!DROP || keep[k][1]) ? y[k].y : 0.0f;
+      v[2 * k] = (km[k] & 0xFFFFu) ? y[k].x : 0.0f;
+      v[2 * k + 1] = (km[k] >> 16) ? y[k].y : 0.0f;
     }
     float4* o4 = reinterpret_cast<float4*>(out);
     __stcs(o4, make_float4(v[0], v[1], v[2], v[3]));
@@ -188,10 +251,18 @@ __device__ __forceinline__ void finish_unit(const uint64_t (&e2)[4], uint64_t g2
 }
 
 // ------------------------------------------------------- warp-per-row kernel
+__device__ __forceinline__ uint32_t hmax2_bits(uint32_t a, uint32_t b) {
+  const __half2 r = __hmax2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // CH = units per lane (row length <= 256*CH).  8 warps per CTA, grid-stride
 // over rows, next row's loads in flight while the current row is processed.
+// FP16 storage keeps the row packed for as long as possible: the maximum and
+// the clamp at lo are taken on half2 words, the widening to FP32 happens once.
 template <typename T, int CH, bool DROP>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
+  constexpr bool HF = sizeof(T) == 2;
   const int lane = threadIdx.x & 31;
   const int L = p.L;
   const long long stride = (long long)gridDim.x * 8;
@@ -211,7 +282,6 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
     else cur[c].fill_neg_inf();
   }
 
-  const uint64_t log2e2 = pack2(kLog2e, kLog2e);
   for (; row < p.rows; row += stride) {
     const long long next_row = row + stride;
 #pragma unroll
@@ -220,32 +290,62 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
       else nxt[c].fill_neg_inf();
     }
 
-    float x[CH][8];
-    float m = -INFINITY;
+    float m;
+    if constexpr (HF) {
+      uint32_t m2 = 0xFC00FC00u;
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      cur[c].widen(x[c]);
+      for (int c = 0; c < CH; ++c) {
+        const uint4 r = cur[c].raw;
+        m2 = hmax2_bits(hmax2_bits(m2, hmax2_bits(r.x, r.y)), hmax2_bits(r.z, r.w));
+      }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) m = fmaxf(m, x[c][i]);
+      for (int off = 16; off >= 1; off >>= 1) m2 = hmax2_bits(m2, __shfl_xor_sync(0xffffffffu, m2, off));
+      const float2 mf = __half22float2(*reinterpret_cast<const __half2*>(&m2));
+      m = fmaxf(mf.x, mf.y);
+    } else {
+      m = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        float x[8];
+        cur[c].widen(x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
+      }
+      m = warp_max(m);
     }
-    m = warp_max(m);
-    if (m == -INFINITY) m = 0.0f;
-    const float negc = -__fmul_rn(m, kLog2e);
-    const uint64_t negc2 = pack2(negc, negc);
+    const bool all_masked = m == -INFINITY;   // defined as an all-zero output row
+    if (all_masked) m = 0.0f;
+    const ExpCtx ctx = make_exp_ctx<HF>(m);
 
     uint64_t e2[CH][4];
     uint64_t s2 = pack2(0.0f, 0.0f);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
+      if constexpr (HF) {
+        const __half lo_h = __float2half_rn(ctx.lo);
+        const __half2 lo2 = __halves2half2(lo_h, lo_h);
+        const uint32_t lo_bits = *reinterpret_cast<const uint32_t*>(&lo2);
+        const uint32_t w[4] = {cur[c].raw.x, cur[c].raw.y, cur[c].raw.z, cur[c].raw.w};
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        e2[c][k] = exp_pair(x[c][2 * k], x[c][2 * k + 1], log2e2, negc2);
-        s2 = add2(s2, e2[c][k]);
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t xw = hmax2_bits(w[k], lo_bits);
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw));
+          e2[c][k] = exp_pair<true, true>(f.x, f.y, ctx);
+          s2 = add2(s2, e2[c][k]);
+        }
+      } else {
+        float x[8];
+        cur[c].widen(x);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          e2[c][k] = exp_pair<false>(x[2 * k], x[2 * k + 1], ctx);
+          s2 = add2(s2, e2[c][k]);
+        }
       }
     }
     const float2 s = unpack2(s2);
     const float total = warp_sum_butterfly(__fadd_rn(s.x, s.y));
-    const float inv = (total == 0.0f) ? 0.0f : __fdiv_rn(1.0f, total);
+    const float inv = (total == 0.0f || all_masked) ? 0.0f : __fdiv_rn(1.0f, total);
     const float g = __fmul_rn(inv, p.keep_scale);
     const uint64_t g2 = pack2(g, g);
 
@@ -267,6 +367,7 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
 // needs 16-byte aligned rows and L % 8 == 0; VEC = 1 takes anything.
 template <typename T, int VEC, bool DROP>
 __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
+  constexpr bool HF = sizeof(T) == 2;
   __shared__ float red[32];
   const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
   const int nwarps = nthr >> 5;
@@ -274,7 +375,6 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
   const int units = (L + VEC - 1) / VEC;
   const T* in = static_cast<const T*>(p.in);
   T* out = static_cast<T*>(p.out);
-  const uint64_t log2e2 = pack2(kLog2e, kLog2e);
 
   for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
     const T* xr = in + row * L;
@@ -296,9 +396,9 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
     m = red[0];
     for (int w = 1; w < nwarps; ++w) m = fmaxf(m, red[w]);
     __syncthreads();
-    if (m == -INFINITY) m = 0.0f;
-    const float negc = -__fmul_rn(m, kLog2e);
-    const uint64_t negc2 = pack2(negc, negc);
+    const bool all_masked = m == -INFINITY;
+    if (all_masked) m = 0.0f;
+    const ExpCtx ctx = make_exp_ctx<HF>(m);
 
     // pass 2: sum of exponentials
     float lane_sum;
@@ -308,7 +408,7 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
         Unit<T> un; un.load(xr + u * 8);
         float x[8]; un.widen(x);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) s2 = add2(s2, exp_pair(x[2 * k], x[2 * k + 1], log2e2, negc2));
+        for (int k = 0; k < 4; ++k) s2 = add2(s2, exp_pair<HF>(x[2 * k], x[2 * k + 1], ctx));
       }
       const float2 s = unpack2(s2);
       lane_sum = __fadd_rn(s.x, s.y);
@@ -316,7 +416,7 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
       float s0 = 0.0f;
       for (int u = tid; u < units; u += nthr) {
         const float xv = (float)xr[u];
-        s0 = __fadd_rn(s0, unpack2(exp_pair(xv, xv, log2e2, negc2)).x);
+        s0 = __fadd_rn(s0, unpack2(exp_pair<HF>(xv, xv, ctx)).x);
       }
       lane_sum = __fadd_rn(s0, 0.0f);
     }
@@ -326,7 +426,7 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
     float total = red[0];
     for (int w = 1; w < nwarps; ++w) total = __fadd_rn(total, red[w]);
     __syncthreads();
-    const float inv = (total == 0.0f) ? 0.0f : __fdiv_rn(1.0f, total);
+    const float inv = (total == 0.0f || all_masked) ? 0.0f : __fdiv_rn(1.0f, total);
     const float g = __fmul_rn(inv, p.keep_scale);
     const uint64_t g2 = pack2(g, g);
 
@@ -338,12 +438,12 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
         float x[8]; un.widen(x);
         uint64_t e2[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) e2[k] = exp_pair(x[2 * k], x[2 * k + 1], log2e2, negc2);
+        for (int k = 0; k < 4; ++k) e2[k] = exp_pair<HF>(x[2 * k], x[2 * k + 1], ctx);
         const long long off = row * L + (long long)u * 8;
         finish_unit<T, DROP>(e2, g2, out + off, p.mask + off, p, (idx0 >> 3) + (unsigned)u);
       } else {
         const float xv = (float)xr[u];
-        const float e = unpack2(exp_pair(xv, xv, log2e2, negc2)).x;
+        const float e = unpack2(exp_pair<HF>(xv, xv, ctx)).x;
         float y = __fmul_rn(e, g);
         unsigned keep = 1u;
         if (DROP) {
@@ -352,7 +452,7 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
           philox_block((uint32_t)(idx >> 3), (uint32_t)(idx >> 35), p.key, o);
           const uint32_t el = (uint32_t)(idx & 7ull);
           const uint32_t word = (el >> 1) == 0 ? o[0] : (el >> 1) == 1 ? o[1] : (el >> 1) == 2 ? o[2] : o[3];
-          keep = ((word >> (16u * (el & 1u))) & 0xFFFFu) >= p.thr;
+          keep = ((word >> (16u * (el & 1u))) & 0x7FFFu) >= p.thr;
           if (!keep) y = 0.0f;
         }
         p.mask[row * L + u] = (unsigned char)keep;
@@ -439,8 +539,10 @@ LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* ma
   SmParams sp;
   sp.in = in; sp.out = out; sp.mask = mask; sp.rows = rows; sp.L = L;
   sp.keep_scale = p >= 1.0f ? 0.0f : 1.0f / (1.0f - p);
-  double t = floor((double)p * 65536.0 + 0.5);
-  sp.thr = p > 0.0f ? (uint32_t)(t > 65536.0 ? 65536.0 : t) : 0u;
+  double t = floor((double)p * 32768.0 + 0.5);
+  sp.thr = p > 0.0f ? (uint32_t)(t > 32768.0 ? 32768.0 : t) : 0u;
+  sp.thr_h2 = (sp.thr & 0xFFFFu) * 0x00010001u;
+  sp.hcmp = sp.thr <= 0x7C00u ? 1 : 0;
   sp.first_row = first_row;
   uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
   for (int r = 0; r < 10; ++r) {

@@ -103,7 +103,7 @@ def test_dropout_mask_statistics_and_sharding(oracle):
     # a shard draws exactly what it would draw as part of the whole
     part = oracle.dropout_mask(4096, p, seed, first_idx=8 * 1000)
     assert np.array_equal(part, m[8000:8000 + 4096])
-    assert oracle.dropout_threshold(0.0) == 0 and oracle.dropout_threshold(1.0) == 65536
+    assert oracle.dropout_threshold(0.0) == 0 and oracle.dropout_threshold(1.0) == 32768
     assert oracle.dropout_mask(64, 1.0, 1).max() == 0 and oracle.dropout_mask(64, 0.0, 1).min() == 1
     # dropout semantics: kept values are softmax / (1 - p), dropped are 0
     x = np.random.default_rng(3).standard_normal((4, 64)).astype(np.float32)
