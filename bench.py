@@ -120,15 +120,16 @@ def cpu_gemm_sample(seconds_target: float = 12.0):
     from tensorfuse_b200 import workloads
     import numpy as np
     A, B, b = _cpu_operands()
-    threads = oracle.max_threads()
+    # every core this process may run on (torchrun sets OMP_NUM_THREADS=1, which is not wanted here)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     pilot = 64
-    t = time.perf_counter(); oracle.gemm_bias_gelu_f16(A[:pilot], B, b); dt = time.perf_counter() - t
+    t = time.perf_counter(); oracle.gemm_bias_gelu_f16(A[:pilot], B, b, threads=threads); dt = time.perf_counter() - t
     rows = int(min(M, max(pilot, pilot * seconds_target / max(dt, 1e-6))))
     rows = max(threads, rows // threads * threads)
     # whole passes over those rows until about seconds_target of CPU time has been spent
     passes, dt = 0, 0.0
     while passes == 0 or (dt < seconds_target * 0.8 and passes < 64):
-        t = time.perf_counter(); out = oracle.gemm_bias_gelu_f16(A[:rows], B, b); dt += time.perf_counter() - t
+        t = time.perf_counter(); out = oracle.gemm_bias_gelu_f16(A[:rows], B, b, threads=threads); dt += time.perf_counter() - t
         passes += 1
     assert np.isfinite(out.astype(np.float32)).all()
     return 2.0 * passes * rows * N * K / dt / 1e12, rows, dt, threads
