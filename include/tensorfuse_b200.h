@@ -117,6 +117,29 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_host(const void* input, void* o
                                                       unsigned char* dropout_mask, long long rows,
                                                       int row_len, int dtype, float dropout_prob,
                                                       unsigned long long seed);
+/* The same operator as tensorfuse_b200_softmax_dropout_host for callers that
+ * must not allocate device memory -- a process whose device memory already
+ * belongs to another allocator or sits at an MPS / MIG cap, or a serving thread
+ * that cannot take the device-wide synchronisation of cudaMalloc / cudaFree.
+ * It has no counterpart in the reference.  Operands are staged in a fixed
+ * 16 MiB area that is part of the library image on every GPU that loads it; no
+ * memory is allocated or freed, on the device or pinned, by this call.
+ *   - limit: 2 * round256(rows*row_len*elem_size) + round256(rows*row_len) must
+ *     not exceed 16 MiB (1-device, whole tensor at once); a larger request
+ *     returns TENSORFUSE_ERROR_OUT_OF_MEMORY and touches nothing;
+ *   - runs on the current device and on `stream`, returns after the results are
+ *     in `output` / `dropout_mask`;
+ *   - the first call on a device looks up the address of the staging area; make
+ *     that first call before any stream capture begins;
+ *   - all calls share the one staging area, whose contents persist from call to
+ *     call: each call overwrites every byte it later reads (nothing has to
+ *     start at zero), but two calls that overlap in time on the same GPU race. */
+TensorFuseStatus tensorfuse_b200_softmax_dropout_host_noalloc(const void* input, void* output,
+                                                              unsigned char* dropout_mask,
+                                                              long long rows, int row_len, int dtype,
+                                                              float dropout_prob,
+                                                              unsigned long long seed,
+                                                              cudaStream_t stream);
 /* Page-locked host memory for the calls above. */
 void* tensorfuse_b200_alloc_pinned(size_t bytes);
 void tensorfuse_b200_free_pinned(void* p);

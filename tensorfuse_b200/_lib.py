@@ -40,7 +40,7 @@ class Config(C.Structure):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m tensorfuse_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python tensorfuse_b200/build.py` "
             "(needs nvcc; there is no CPU or PyTorch fallback)")
     L = C.CDLL(LIB_PATH)
     vp, i, f, ll, ull, st = C.c_void_p, C.c_int, C.c_float, C.c_longlong, C.c_ulonglong, C.c_void_p
@@ -82,6 +82,7 @@ def _load():
     sig("tensorfuse_b200_last_softmax_seed", ull, [])
     sig("tensorfuse_b200_gemm_bias_gelu_host", i, [vp, vp, vp, vp, i, i, i, i, i, i, i, f, f])
     sig("tensorfuse_b200_softmax_dropout_host", i, [vp, vp, vp, ll, i, i, f, ull])
+    sig("tensorfuse_b200_softmax_dropout_host_noalloc", i, [vp, vp, vp, ll, i, i, f, ull, st])
     sig("tensorfuse_b200_alloc_pinned", vp, [C.c_size_t])
     sig("tensorfuse_b200_free_pinned", None, [vp])
     sig("tensorfuse_b200_plan_shards", None, [ll, i, i, C.POINTER(ll), C.POINTER(ll)])

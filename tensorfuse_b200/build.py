@@ -1,6 +1,6 @@
 """Compile libtensorfuse.so (sm_100a only) in-tree with nvcc.
 
-    python -m tensorfuse_b200.build [--force]
+    python tensorfuse_b200/build.py [--force]
 
 The shared library lands in tensorfuse_b200/lib/ and is what both the ctypes
 layer of this package and a C/C++ caller link against.  nvcc cross-compiles, so
@@ -22,7 +22,7 @@ OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "libtensorfuse.so")
 
 SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "runtime.cpp", "c_api.cpp",
-           "host_ops.cpp"]
+           "host_ops.cpp", "noalloc.cu"]
 HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
