@@ -404,6 +404,26 @@ def side_workloads(tf, L, dev, peaks, args):
                          "frac_of_nominal_4500": tops / NOMINAL["int8_tops"]}}
     except Exception as e:
         out["int8_gemm_error"] = repr(e)
+
+    # --- context only: the vendor library on the headline shape (not the product path)
+    try:
+        sets = 4
+        As = [torch.randn((M, K), device=dev).half() for _ in range(sets)]
+        Bm = (torch.randn((K, N), device=dev) / 32).half()
+        bv = (torch.randn(N, device=dev) * 0.02).half()
+        Cs = [torch.empty((M, N), dtype=torch.float16, device=dev) for _ in range(sets)]
+        avg, _ = timed(lambda i: torch.matmul(As[i % sets], Bm, out=Cs[i % sets]), steps)
+
+        def unfused(i):
+            torch.addmm(bv, As[i % sets], Bm, out=Cs[i % sets])
+            torch.nn.functional.gelu(Cs[i % sets], approximate="tanh")
+        avg2, _ = timed(unfused, steps)
+        out["library_same_shape_fp16"] = {
+            "note": "cuBLAS through torch on M 16384 K 1024 N 4096, for context; not part of this library",
+            "matmul_only_tflops": FLOP_PER_STEP / (avg * 1e-3) / 1e12,
+            "addmm_then_gelu_tflops": FLOP_PER_STEP / (avg2 * 1e-3) / 1e12}
+    except Exception as e:
+        out["library_same_shape_error"] = repr(e)
     return out
 
 
