@@ -22,7 +22,7 @@ OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "libtensorfuse.so")
 
 SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "runtime.cpp", "c_api.cpp",
-           "host_ops.cpp", "noalloc.cu"]
+           "host_ops.cpp", "noalloc.cu", "profiler.cpp"]
 HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -12,7 +12,7 @@ INC = os.path.join(ROOT, "include")
 
 def _declared_functions():
     names = set()
-    for rel in ("tensorfuse/tensorfuse.h", "tensorfuse_b200.h"):
+    for rel in ("tensorfuse/tensorfuse.h", "tensorfuse/profiler.h", "tensorfuse_b200.h"):
         src = open(os.path.join(INC, rel)).read()
         src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
         for m in re.finditer(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\(", src):
@@ -78,3 +78,38 @@ def test_product_does_not_import_the_oracle():
                 assert "oracle" not in text.lower() or f in ("softmax_dropout.cu", "kernels.h"), (dirpath, f)
     code = "import sys; import tensorfuse_b200; assert not any(m.startswith('oracle') for m in sys.modules)"
     subprocess.run([sys.executable, "-c", code], check=True, cwd=ROOT)
+
+
+def test_profiler_helpers_measure_something(tmp_path):
+    """Host-side helpers of tensorfuse/profiler.h (placeholders in the reference,
+    src/tensorfuse_c_api.cpp:462-643): timers and the roofline arithmetic need no GPU."""
+    import time
+    from tensorfuse_b200._lib import LIB_PATH
+
+    class Timer(C.Structure):
+        _fields_ = [("start_time", C.c_double), ("end_time", C.c_double), ("running", C.c_bool)]
+
+    class Roofline(C.Structure):
+        _fields_ = [(n, C.c_float) for n in ("peak_flops", "peak_bandwidth", "arithmetic_intensity", "achieved_flops",
+                                             "achieved_bandwidth", "efficiency_flops", "efficiency_bandwidth")] + \
+                   [("is_compute_bound", C.c_bool), ("is_memory_bound", C.c_bool)]
+
+    lib = C.CDLL(LIB_PATH)
+    lib.tensorfuse_timer_elapsed_ms.restype = C.c_double
+    t = Timer()
+    lib.tensorfuse_timer_start(C.byref(t)); time.sleep(0.02); lib.tensorfuse_timer_stop(C.byref(t))
+    assert 15.0 < lib.tensorfuse_timer_elapsed_ms(C.byref(t)) < 500.0
+    lib.tensorfuse_calculate_roofline.argtypes = [C.c_size_t, C.c_size_t, C.c_float, C.POINTER(Roofline)]
+    r = Roofline()
+    # config 2: 137.44 GFLOP over 176.2 MB in 0.1 ms
+    assert lib.tensorfuse_calculate_roofline(137438953472, 176168960, 0.1, C.byref(r)) == 0
+    assert r.is_compute_bound and not r.is_memory_bound and abs(r.achieved_flops / 1.374e15 - 1) < 1e-3
+    assert abs(r.efficiency_flops - 61.08) < 0.1
+    assert lib.tensorfuse_calculate_roofline(1, 1, 0.1, None) == 1
+    rid = lib.tensorfuse_profiler_start_region(b"step", b"test")
+    assert rid >= 1 and lib.tensorfuse_profiler_end_region(rid) == 0 and lib.tensorfuse_profiler_end_region(10 ** 6) == 1
+    out = tmp_path / "prof.json"
+    assert lib.tensorfuse_profiler_save(str(out).encode(), b"json") == 0
+    import json
+    assert json.load(open(out))["regions"][-1]["name"] == "step"
+    assert lib.tensorfuse_profiler_reset() == 0
