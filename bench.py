@@ -474,8 +474,73 @@ def run_only(args):
     return 0
 
 
+def run_encoder(args):
+    """Config 5: BERT-large encoder forward (24 layers, hidden 1024, 16 heads, FFN 4096,
+    FP16, random weights), batch 256 x seq 512 split by batch over the ranks (strong
+    scaling, replicated weights, no data-path collective).  One JSON line: tokens/s."""
+    import torch
+    import torch.distributed as dist
+    import tensorfuse_b200 as tf
+    from tensorfuse_b200 import bert_encoder as be
+
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    tf.init()
+    dev = torch.device("cuda", local)
+    cfg = be.EncoderConfig()
+    batch, seq = 256, 512
+    b_local = batch // world
+    layers = be.random_weights(cfg, dev, seed=4)
+    g = torch.Generator(device="cpu"); g.manual_seed(4 + rank)
+    x = torch.randn((b_local, seq, cfg.hidden), generator=g).to(dev, torch.float16)
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    steps, warm = max(1, min(args.steps, 10)), max(1, min(args.warmup, 3))
+    with torch.no_grad():
+        for i in range(warm):
+            be.encoder_forward(x, layers, cfg, seed=i)
+        sync()
+        launches0 = tf.launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            y = be.encoder_forward(x, layers, cfg, seed=100 + i)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX); ms = float(t.item())
+        dist.barrier(); dist.destroy_process_group()
+    if rank != 0:
+        return 0
+    assert bool(torch.isfinite(y).all()) and tf.watchdog_status() == 0
+    tokens = batch * seq
+    flop = 27.26e6 * tokens * cfg.layers       # 27.26 MFLOP per token per layer
+    print(json.dumps({
+        "metric": "bert_large_encoder_forward_tokens_per_s", "value": tokens / (ms * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": "bert_large_encoder_forward", "layers": 24, "hidden": 1024, "heads": 16, "ffn": 4096,
+                   "global_batch": batch, "seq_len": seq, "parallelism": f"dp{world}_batch_sharded_replicated_weights",
+                   "fused_ops": "softmax+dropout p=0.1 (attention probabilities), FFN-up GEMM+bias+GELU, FFN-down GEMM+bias",
+                   "other_ops": "torch (cuBLAS projections and attention matmuls, layer norm)"},
+        "effective_tflops": flop / (ms * 1e-3) / 1e12,
+        "gpu_launches": int(tf.launch_count() - launches0)}), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="gemm_fp16", choices=["gemm_fp16", "bert_large"],
+                    help="gemm_fp16 = the headline (default); bert_large = encoder forward, tokens/s")
     ap.add_argument("--only", default=None, choices=["gemm_fp16", "gemm_int8", "softmax", "softmax_p0"],
                     help="run a single kernel a few times (profiling aid)")
     ap.add_argument("--gpus", type=int, default=1)
@@ -487,6 +552,8 @@ def main():
         return run_reference(args)
     if args.only:
         return run_only(args)
+    if args.workload == "bert_large":
+        return run_encoder(args)
     return run_gpu(args)
 
 

@@ -77,6 +77,16 @@ TensorFuseStatus tensorfuse_b200_gemm_int8(const void* A, const void* B, const v
                                            int bias_dtype, int out_dtype, int epilogue,
                                            cudaStream_t stream);
 
+/* C = act(alpha * A[M,K] * B[K,N] + beta * bias[N]) for FP16 or FP32 operands
+ * (dtype), activation = TENSORFUSE_ACTIVATION_GELU or TENSORFUSE_ACTIVATION_NONE.
+ * NONE is the FFN-down form: the reference's benchmark applies GELU to that
+ * projection too because its only entry point always does
+ * (benchmarks/bert_baseline.cu:318-322); the activation enum is the reference's
+ * (src/tensorfuse/types.h:74-81). */
+TensorFuseStatus tensorfuse_b200_gemm_bias_act(const void* A, const void* B, const void* bias, void* C,
+                                               int M, int N, int K, int dtype, int activation,
+                                               float alpha, float beta, cudaStream_t stream);
+
 /* Row-sharded softmax+dropout: `rows` rows of length `row_len`; `first_row`
  * is the index of the first of them inside the whole tensor, so that a shard
  * draws exactly the dropout decisions it would get as part of the whole.

@@ -396,6 +396,17 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_rows(const void* input, void* o
                                           dropout_prob, seed, first_row, stream));
 }
 
+TensorFuseStatus tensorfuse_b200_gemm_bias_act(const void* A, const void* B, const void* bias, void* C, int M,
+                                             int N, int K, int dtype, int activation, float alpha, float beta,
+                                             cudaStream_t stream) {
+  if (dtype != kF16 && dtype != kF32) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  int epi;
+  if (activation == TENSORFUSE_ACTIVATION_GELU) epi = kEpiGelu;
+  else if (activation == TENSORFUSE_ACTIVATION_NONE) epi = kEpiLinear;
+  else return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  return gemm_flat(A, B, bias, C, M, N, K, dtype, dtype, dtype, epi, alpha, beta, 1.0f, nullptr, nullptr, stream);
+}
+
 void tensorfuse_b200_softmax_schedule(int row_len, int dtype, int aligned16, int* vec, int* warps) {
   const SoftmaxSchedule s = softmax_schedule(row_len, dtype, aligned16 != 0);
   if (vec) *vec = s.vec;

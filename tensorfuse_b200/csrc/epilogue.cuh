@@ -65,7 +65,9 @@ template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return _
 // Returns the value to store, still in FP32 (or the raw integer through a bit cast).
 template <int EPI, bool FP32_OUT, typename AccT>
 __device__ __forceinline__ float epilogue_value(AccT acc, float bias, const EpiParams& ep) {
-  if constexpr (EPI == kEpiGelu) {
+  if constexpr (EPI == kEpiLinear) {
+    return ep.alpha * (float)acc + ep.beta * bias;
+  } else if constexpr (EPI == kEpiGelu) {
     const float x = ep.alpha * (float)acc + ep.beta * bias;
     return FP32_OUT ? gelu_accurate(x) : gelu_fast(x);
   } else if constexpr (EPI == kEpiI8Dequant) {

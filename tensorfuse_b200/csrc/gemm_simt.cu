@@ -123,6 +123,10 @@ LaunchResult launch_gemm_simt(const GemmArgs& a, cudaStream_t stream) {
     return run<float, float, kEpiGelu>(a, stream);
   if (a.in_dtype == kF16 && a.out_dtype == kF16 && a.epilogue == kEpiGelu)
     return run<__half, __half, kEpiGelu>(a, stream);
+  if (a.in_dtype == kF32 && a.out_dtype == kF32 && a.epilogue == kEpiLinear)
+    return run<float, float, kEpiLinear>(a, stream);
+  if (a.in_dtype == kF16 && a.out_dtype == kF16 && a.epilogue == kEpiLinear)
+    return run<__half, __half, kEpiLinear>(a, stream);
   if (a.in_dtype == kI8) {
     if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF16) return run<int8_t, __half, kEpiI8Dequant>(a, stream);
     if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF32) return run<int8_t, float, kEpiI8Dequant>(a, stream);

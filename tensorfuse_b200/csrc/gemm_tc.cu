@@ -137,7 +137,7 @@ bool gemm_tc_eligible(const GemmArgs& a) {
   const uintptr_t ptrs = (uintptr_t)a.A | (uintptr_t)a.B | (uintptr_t)a.C;
   if (ptrs & 15u) return false;
   if (((size_t)a.K * es) % 16 || ((size_t)a.N * es) % 16 || ((size_t)a.N * out_es) % 16) return false;
-  if (a.in_dtype == kF16) return a.out_dtype == kF16 && a.epilogue == kEpiGelu;
+  if (a.in_dtype == kF16) return a.out_dtype == kF16 && (a.epilogue == kEpiGelu || a.epilogue == kEpiLinear);
   return (a.epilogue == kEpiI8Dequant && (a.out_dtype == kF16 || a.out_dtype == kF32)) ||
          (a.epilogue == kEpiI8Legacy && a.out_dtype == kF32) ||
          (a.epilogue == kEpiI8Raw && a.out_dtype == kI32);
@@ -146,6 +146,7 @@ bool gemm_tc_eligible(const GemmArgs& a) {
 LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   if (!gemm_tc_eligible(a)) return kUnsupported;
   if (!a.bias && a.epilogue != kEpiI8Raw) return kInvalidArgument;
+  if (a.in_dtype == kF16 && a.epilogue == kEpiLinear) return run<0, kEpiLinear, __half>(a, stream);
   if (a.in_dtype == kF16) return run<0, kEpiGelu, __half>(a, stream);
   if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF16) return run<1, kEpiI8Dequant, __half>(a, stream);
   if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF32) return run<1, kEpiI8Dequant, float>(a, stream);

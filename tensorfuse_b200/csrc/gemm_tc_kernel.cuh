@@ -126,13 +126,14 @@ __device__ __forceinline__ void staging_store16(uint32_t base, int row, int j, u
 // gelu(x) = x / (1 + 2^(-x (k1 + k2 x^2))).
 template <int EPI, bool FP32_OUT, bool INT_ACC>
 __device__ __forceinline__ float2 epilogue_pair(uint32_t r0, uint32_t r1, float b0, float b1, const EpiParams& ep) {
-  if constexpr (!FP32_OUT && (EPI == kEpiGelu || EPI == kEpiI8Dequant)) {
+  if constexpr (!FP32_OUT && (EPI == kEpiGelu || EPI == kEpiI8Dequant || EPI == kEpiLinear)) {
     float a0, a1;
     if constexpr (INT_ACC) { a0 = (float)(int)r0; a1 = (float)(int)r1; }
     else { a0 = __uint_as_float(r0); a1 = __uint_as_float(r1); }
     uint64_t x2;
-    if constexpr (EPI == kEpiGelu) x2 = fma2(pack2(a0, a1), pack2(ep.alpha, ep.alpha), pack2(ep.beta * b0, ep.beta * b1));
+    if constexpr (EPI == kEpiGelu || EPI == kEpiLinear) x2 = fma2(pack2(a0, a1), pack2(ep.alpha, ep.alpha), pack2(ep.beta * b0, ep.beta * b1));
     else x2 = fma2(pack2(a0, a1), pack2(ep.scale, ep.scale), pack2(b0, b1));
+    if constexpr (EPI == kEpiLinear) return unpack2(x2);
     const float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
     const float k2 = k1 * 0.044715f;
     const uint64_t w2 = fma2(mul2(x2, x2), pack2(k2, k2), pack2(k1, k1));

@@ -42,6 +42,7 @@ enum Epilogue : int {
   kEpiI8Dequant = 1,   // out = gelu(fma(float(acc), scale, bias))          (INT8, multiply convention)
   kEpiI8Legacy = 2,    // out = gelu_clamped(acc/scale + bias)*scale, non-finite -> 0 (INT8, reference convention)
   kEpiI8Raw = 3,       // out = acc (INT32), no bias, no activation
+  kEpiLinear = 4,      // out = alpha*acc + beta*bias, no activation        (FP32 / FP16 paths, e.g. FFN-down)
 };
 
 struct GemmArgs {

@@ -251,3 +251,31 @@ def test_int8_full_size_sampled(tf, oracle):
                                        int(DT.FLOAT32), int(DT.INT32), tf.INT8_RAW, stream()) == 0
     check_watchdog()
     assert np.array_equal(host(dI[torch.from_numpy(rows).cuda()]), acc)
+
+
+# ------------------------------------------------------- linear epilogue
+@pytest.mark.parametrize("dtype,M,N,K", [(np.float16, 384, 512, 256), (np.float16, 100, 264, 72),
+                                         (np.float16, 33, 17, 9), (np.float32, 65, 70, 33)])
+def test_bias_only_epilogue(tf, dtype, M, N, K):
+    """activation NONE (the FFN-down form): alpha*A*B + beta*bias without GELU."""
+    from gpu_util import DT, L, check_watchdog, dev, host, stream
+    r = np.random.default_rng(M)
+    A = r.standard_normal((M, K)).astype(dtype)
+    B = (r.standard_normal((K, N)) / np.sqrt(K)).astype(dtype)
+    b = (r.standard_normal(N) * 0.1).astype(dtype)
+    dA, dB, db = dev(A), dev(B), dev(b)
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    for act, alpha, beta in ((0, 1.0, 1.0), (0, 0.125, 0.0), (2, 1.0, 1.0)):
+        dC = torch.zeros((M, N), dtype=tdt, device="cuda")
+        st = L.tensorfuse_b200_gemm_bias_act(dA.data_ptr(), dB.data_ptr(), db.data_ptr(), dC.data_ptr(), M, N, K,
+                                             int(DT.FLOAT16 if dtype == np.float16 else DT.FLOAT32), act, alpha, beta,
+                                             stream())
+        check_watchdog()
+        assert st == 0
+        lin = alpha * (A.astype(np.float64) @ B.astype(np.float64)) + beta * b.astype(np.float64)
+        want = lin if act == 0 else lin * 0.5 * (1 + np.tanh(0.7978845608028654 * (lin + 0.044715 * lin ** 3)))
+        got = host(dC).astype(np.float64)
+        tol_r, tol_a = (1e-2, 1e-3) if dtype == np.float16 else (1e-4, 1e-4)
+        assert np.all(np.abs(got - want) <= tol_a + tol_r * np.abs(want))
+    assert L.tensorfuse_b200_gemm_bias_act(dA.data_ptr(), dB.data_ptr(), db.data_ptr(), dC.data_ptr(), M, N, K,
+                                           int(DT.FLOAT16 if dtype == np.float16 else DT.FLOAT32), 1, 1.0, 1.0, None) == 10
