@@ -87,6 +87,27 @@ TensorFuseStatus tensorfuse_b200_gemm_bias_act(const void* A, const void* B, con
                                                int M, int N, int K, int dtype, int activation,
                                                float alpha, float beta, cudaStream_t stream);
 
+/* Scaled-dot-product attention over heads, fused (the computation behind
+ * tensorfuse_fused_multi_head_attention, which the reference leaves as a
+ * placeholder: src/tensorfuse_c_api.cpp:288-311):
+ *   out[b,i,h,:] = sum_j keep_j/(1-p) * softmax_j(scale * q[b,i,h,:].k[b,j,h,:]) * v[b,j,h,:]
+ * Element (b, s, h, c) of a tensor is at base + b*bs + s*ld + h*hs + c, strides
+ * in elements; hs = 0 means head_dim and bs = 0 means seq*ld, i.e. rows of
+ * [batch, seq, heads*head_dim] (a fused QKV buffer is ld = 3*hidden with three
+ * base pointers).  scale <= 0 selects 1/sqrt(head_dim).  kv_lengths (device,
+ * `batch` ints, may be NULL) masks keys j >= kv_lengths[b]; a row without a
+ * valid key yields zeros.  Dropout decisions are those the softmax+dropout
+ * operator makes for a [batch, heads, seq_q, seq_kv] tensor with the same seed.
+ * FP16 with head_dim 64 and 16-byte aligned pointers / strides runs on the
+ * tensor cores; other FP16 / FP32 shapes (head_dim <= 256) on CUDA cores. */
+TensorFuseStatus tensorfuse_b200_attention(const void* q, const void* k, const void* v, void* out, int batch,
+                                           int seq_q, int seq_kv, int heads, int head_dim, long long ld_q,
+                                           long long ld_k, long long ld_v, long long ld_o, long long hs_q,
+                                           long long hs_k, long long hs_v, long long hs_o, long long bs_q,
+                                           long long bs_k, long long bs_v, long long bs_o, int dtype,
+                                           float scale, float dropout_prob, unsigned long long seed,
+                                           const int* kv_lengths, cudaStream_t stream);
+
 /* Row-sharded softmax+dropout: `rows` rows of length `row_len`; `first_row`
  * is the index of the first of them inside the whole tensor, so that a shard
  * draws exactly the dropout decisions it would get as part of the whole.

@@ -389,5 +389,59 @@ void tfo_softmax_dropout_exact(const void* in, void* out, uint8_t* mask, long ro
 
 /* ---------------------------------------------------------------- helpers */
 
+/* ------------------------------------------------- multi-head attention
+ * The reference only declares this operator (src/tensorfuse/tensorfuse.h:90-114:
+ * query/key/value/output [batch, seq, hidden], heads split hidden, dropout on
+ * the attention weights) and leaves its body empty (src/tensorfuse_c_api.cpp:
+ * 288-311), so there is nothing of the reference's to pin this against: the
+ * restatement composes the reference's own softmax_ref / dropout_ref semantics
+ * (src/tests/test_softmax_dropout.cu:36-79) with two plain matrix products.
+ *   out[b,i,h,:] = sum_j keep/(1-p) * softmax_j(scale * q[b,i,h,:].k[b,j,h,:]) * v[b,j,h,:]
+ * Inputs FP32 [batch, seq, heads*hd] (FP16 callers widen first), FP32 scores,
+ * double accumulation of the weighted sum; keys j >= kv_len[b] are masked; the
+ * keep decision of (b,h,i,j) is dropout_keep(((b*heads+h)*seq_q+i)*seq_kv+j). */
+void tfo_attention_f32(const float* q, const float* k, const float* v, float* out, int batch,
+                       int seq_q, int seq_kv, int heads, int hd, float scale, float p, uint64_t seed,
+                       const int* kv_len, int threads) {
+  set_threads(threads);
+  const uint32_t thr = tfo_dropout_threshold(p);
+  const float ks = p >= 1.0f ? 0.0f : 1.0f / (1.0f - p);
+  const long hidden = (long)heads * hd;
+  const long rows = (long)batch * heads * seq_q;
+#pragma omp parallel
+  {
+    float* sc = (float*)malloc(sizeof(float) * (size_t)(seq_kv > 0 ? seq_kv : 1));
+    double* acc = (double*)malloc(sizeof(double) * (size_t)hd);
+#pragma omp for schedule(static)
+    for (long r = 0; r < rows; ++r) {
+      const int i = (int)(r % seq_q), h = (int)((r / seq_q) % heads), b = (int)(r / ((long)seq_q * heads));
+      int n = seq_kv;
+      if (kv_len) { n = kv_len[b] < n ? kv_len[b] : n; if (n < 0) n = 0; }
+      const float* qr = q + ((long)b * seq_q + i) * hidden + (long)h * hd;
+      float* o = out + ((long)b * seq_q + i) * hidden + (long)h * hd;
+      float mx = -INFINITY;
+      for (int j = 0; j < n; ++j) {
+        const float* kr = k + ((long)b * seq_kv + j) * hidden + (long)h * hd;
+        float d = 0.0f;
+        for (int c = 0; c < hd; ++c) d += qr[c] * kr[c];
+        sc[j] = d * scale;
+        mx = fmaxf(mx, sc[j]);
+      }
+      float sum = 0.0f;
+      for (int j = 0; j < n; ++j) { sc[j] = expf(sc[j] - mx); sum += sc[j]; }
+      for (int c = 0; c < hd; ++c) acc[c] = 0.0;
+      for (int j = 0; j < n; ++j) {
+        if (thr != 0 && !dropout_keep((uint64_t)r * (uint64_t)seq_kv + (uint64_t)j, seed, thr)) continue;
+        const float w = sc[j] / sum * ks;
+        const float* vr = v + ((long)b * seq_kv + j) * hidden + (long)h * hd;
+        for (int c = 0; c < hd; ++c) acc[c] += (double)w * vr[c];
+      }
+      for (int c = 0; c < hd; ++c) o[c] = n > 0 ? (float)acc[c] : 0.0f;
+    }
+    free(sc);
+    free(acc);
+  }
+}
+
 void tfo_f32_to_f16(const float* src, uint16_t* dst, long n) { for (long i = 0; i < n; ++i) dst[i] = f2h(src[i]); }
 void tfo_f16_to_f32(const uint16_t* src, float* dst, long n) { for (long i = 0; i < n; ++i) dst[i] = h2f(src[i]); }

@@ -59,6 +59,7 @@ def lib():
         L.tfo_dropout_threshold.argtypes = [f]
         L.tfo_dropout_mask.argtypes = [vp, u64, l, f, u64]
         L.tfo_softmax_dropout_exact.argtypes = [vp, vp, vp, l, i, i, f, u64, u64, i, i, i]
+        L.tfo_attention_f32.argtypes = [vp, vp, vp, vp, i, i, i, i, i, f, f, u64, vp, i]
         _lib = L
     return _lib
 
@@ -172,6 +173,22 @@ def softmax_dropout_exact(x, p=0.0, seed=0, first_row=0, vec=8, warps=1, threads
                                     1 if x.dtype == np.float16 else 0, p, seed, first_row,
                                     vec, warps, threads)
     return out, mask
+
+
+def attention(q, k, v, heads, p=0.0, seed=0, scale=None, kv_lengths=None, threads=0):
+    """Multi-head scaled-dot-product attention with dropout on the weights;
+    q [batch, seq_q, hidden], k/v [batch, seq_kv, hidden] (FP16 or FP32, widened
+    to FP32), returns FP32 [batch, seq_q, hidden]."""
+    q32, k32, v32 = (np.ascontiguousarray(t, np.float32) for t in (q, k, v))
+    B, Sq, Hd = q32.shape
+    Skv = k32.shape[1]
+    hd = Hd // heads
+    out = np.empty_like(q32)
+    lens = None if kv_lengths is None else np.ascontiguousarray(kv_lengths, np.int32)
+    lib().tfo_attention_f32(_p(q32), _p(k32), _p(v32), _p(out), B, Sq, Skv, heads, hd,
+                            float(scale if scale else 1.0 / np.sqrt(hd)), float(p), int(seed),
+                            None if lens is None else _p(lens), threads)
+    return out
 
 
 # -------------------------------------------------------------- numpy twins

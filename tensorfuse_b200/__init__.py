@@ -447,17 +447,62 @@ def _softmax_torch_cuda(x, out, mask, p, stream, seed):
     return out, mask
 
 
-def fused_multi_head_attention(query, key, value, output, num_heads, dropout_prob=0.0, stream=None):
-    """Argument validation only, exactly like the reference entry point
-    (src/tensorfuse_c_api.cpp:288-311 computes nothing)."""
-    def as_c(t):
-        if _is_torch(t):
-            return _c_tensor(t.data_ptr(), tuple(t.shape), _torch_dt(t))
-        a = np.ascontiguousarray(t)
-        return _c_tensor(a.ctypes.data, a.shape, _NP_TO_DT[a.dtype])
-    q, k, v, o = as_c(query), as_c(key), as_c(value), as_c(output)
-    st = _auto_init(_L.tensorfuse_fused_multi_head_attention, C.byref(q), C.byref(k), C.byref(v),
-                    C.byref(o), int(num_heads), float(dropout_prob), None)
+def fused_multi_head_attention(query, key, value, output=None, num_heads=1, dropout_prob=0.0, stream=None, *,
+                               seed=None, kv_lengths=None, scale=None):
+    """output = dropout(softmax(scale * Q K^T)) V per head; query/output
+    [batch, seq_q, hidden], key/value [batch, seq_kv, hidden], heads split hidden.
+
+    Reference signature: fused_multi_head_attention(query, key, value, output,
+    num_heads, dropout_prob, stream) (core_bindings.cpp:773-795), whose C entry
+    only validates (src/tensorfuse_c_api.cpp:288-311); this one computes.  torch
+    CUDA tensors run in place (last dimension contiguous; a view into a fused
+    QKV buffer is fine); numpy arrays are staged through the device.  ``seed``
+    fixes the dropout decisions, ``kv_lengths`` (one int per batch item) masks
+    the keys from that position on, ``scale`` defaults to 1/sqrt(head width).
+    """
+    import torch
+    if not _is_torch(query):
+        if not torch.cuda.is_available():
+            raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(Status.CUDA_ERROR))
+        q, k, v = (torch.from_numpy(np.ascontiguousarray(t)).cuda() for t in (query, key, value))
+        lens = None if kv_lengths is None else torch.as_tensor(np.asarray(kv_lengths, np.int32)).cuda()
+        o = fused_multi_head_attention(q, k, v, None, num_heads, dropout_prob, None, seed=seed,
+                                       kv_lengths=lens, scale=scale)
+        res = o.cpu().numpy()
+        if output is not None:
+            output[...] = res
+            return output
+        return res
+    q, k, v = query, key, value
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3 or num_heads <= 0 or q.shape[2] % max(num_heads, 1):
+        raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(
+            Status.INVALID_ARGUMENT if num_heads <= 0 else Status.INVALID_TENSOR_SHAPE))
+    if k.shape != v.shape or k.shape[0] != q.shape[0] or k.shape[2] != q.shape[2]:
+        raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(Status.INVALID_TENSOR_SHAPE))
+    q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
+    if output is None:
+        output = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    if output.shape != q.shape or output.stride(-1) != 1 or output.dtype != q.dtype:
+        raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(Status.INVALID_TENSOR_SHAPE))
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(Status.INVALID_ARGUMENT))
+    dt = _torch_dt(q)
+    if dt not in (DataType.FLOAT16, DataType.FLOAT32):
+        raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(Status.UNSUPPORTED_OPERATION))
+    lens_ptr = None
+    if kv_lengths is not None:
+        kv_lengths = torch.as_tensor(kv_lengths, dtype=torch.int32, device=q.device).contiguous()
+        lens_ptr = kv_lengths.data_ptr()
+    if seed is None:
+        seed = _next_host_seed()
+    B, Sq, H = q.shape
+    hd = H // num_heads
+    with torch.cuda.device(q.device):
+        st = _auto_init(_L.tensorfuse_b200_attention, q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(),
+                        B, Sq, k.shape[1], int(num_heads), hd, q.stride(1), k.stride(1), v.stride(1), output.stride(1),
+                        0, 0, 0, 0, q.stride(0), k.stride(0), v.stride(0), output.stride(0), int(dt),
+                        float(scale or 0.0), float(dropout_prob), int(seed) & 0xFFFFFFFFFFFFFFFF, lens_ptr,
+                        _torch_stream(stream, q.device))
     _check("fused_multi_head_attention", st)
     return output
 

@@ -77,6 +77,7 @@ def _load():
     sig("fused_softmax_dropout_fp32_wrapper", i, sm)
     sig("tensorfuse_b200_gemm_int8", i, [vp, vp, vp, vp, i, i, i, f, f, i, i, i, st])
     sig("tensorfuse_b200_gemm_bias_act", i, [vp, vp, vp, vp, i, i, i, i, i, f, f, st])
+    sig("tensorfuse_b200_attention", i, [vp, vp, vp, vp, i, i, i, i, i] + [ll] * 12 + [i, f, f, ull, vp, st])
     sig("tensorfuse_b200_softmax_dropout_rows", i, [vp, vp, vp, ll, i, i, f, ull, ull, st])
     sig("tensorfuse_b200_softmax_schedule", None, [i, i, i, C.POINTER(i), C.POINTER(i)])
     sig("tensorfuse_b200_set_random_seed", None, [ull])

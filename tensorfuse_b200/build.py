@@ -21,9 +21,9 @@ LIBDIR = os.path.join(PKG, "lib")
 OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "libtensorfuse.so")
 
-SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "runtime.cpp", "c_api.cpp",
+SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "runtime.cpp", "c_api.cpp",
            "host_ops.cpp", "noalloc.cu", "profiler.cpp"]
-HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh"]
+HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh", "attention_tc_kernel.cuh", "philox.cuh", "tma_host.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=default", "-DTENSORFUSE_WITH_CUDA_RUNTIME",

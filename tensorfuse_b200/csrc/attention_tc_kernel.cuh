@@ -1,0 +1,359 @@
+// attention_tc_kernel.cuh -- device side of the fused multi-head attention
+// forward for FP16 tensors with 64-wide heads:
+//     out = dropout(softmax(scale * Q K^T)) V     per (batch item, head)
+// The probabilities never reach device memory.  (The reference declares this
+// operator and leaves it empty: reference src/tensorfuse_c_api.cpp:288-311.)
+//
+// One CTA owns 128 query rows of one head and walks the keys in blocks of 128;
+// two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns each), so one
+// CTA's softmax arithmetic overlaps the other's tensor-core work.
+//   warp 0, one lane : TMA producer.  Q once; K and V blocks into a 2-deep ring
+//                      of 128-byte-swizzled boxes (4-D tensor maps: any batch /
+//                      sequence / head strides, zero fill past the sequence end).
+//   warp 1, one lane : tcgen05.mma issuer.  S = Q K_j^T (M 128, N 128, K 64: both
+//                      operands K-major) into TMEM columns 0..127; O += P_j V_j
+//                      (M 128, N 64, K 128: P K-major from shared memory, V as
+//                      stored, i.e. MN-major) into columns 128..191.  S_{j+1} is
+//                      issued as soon as the softmax warps have read S_j.
+//   warps 2-5        : softmax.  Thread = query row = TMEM lane, so row maxima
+//                      and sums need no shuffles.  Pass 1 reads the 128 scores
+//                      of the row for the block maximum; pass 2 reads them again,
+//                      exponentiates in the base-2 domain (scale * log2 e folded
+//                      into one FMA), applies the dropout decisions, and writes
+//                      FP16 probabilities to the swizzled P tile.  When the
+//                      running maximum moves, the same thread rescales its O row
+//                      in TMEM (tcgen05.ld / st) before releasing P to the MMA
+//                      issuer.  The final O row is divided by the row sum, scaled
+//                      by 1/(1-p), converted and stored through TMA.
+// Every mbarrier wait is bounded (ptx.cuh): an expired wait raises the CTA abort
+// flag, records a code in the watchdog word, and all roles fall through to the
+// tear-down that frees TMEM.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include "kernels.h"
+#include "philox.cuh"
+#include "ptx.cuh"
+
+namespace tfb {
+namespace attn {
+
+constexpr int BQ = 128;    // query rows per CTA
+constexpr int BKV = 128;   // keys per block
+constexpr int HD = 64;     // head width
+constexpr int KV_STAGES = 2;
+constexpr int TILE_BYTES = 128 * 128;          // 128 rows of 64 FP16
+constexpr int NUM_THREADS = 192;
+constexpr int SOFTMAX_THREADS = 128;
+constexpr int TMEM_COLS = 256;                 // S: 0..127, O: 128..191
+constexpr int OFF_Q = 0;
+constexpr int OFF_K = OFF_Q + TILE_BYTES;
+constexpr int OFF_V = OFF_K + KV_STAGES * TILE_BYTES;
+constexpr int OFF_P = OFF_V + KV_STAGES * TILE_BYTES;   // two boxes: keys 0..63, 64..127
+constexpr int OFF_BAR = OFF_P + 2 * TILE_BYTES;
+// barriers: q, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_free, p_full, o_done
+constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 4;
+constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+constexpr int SMEM_BYTES = OFF_MISC + 16;
+static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs per SM");
+
+// watchdog codes of this kernel
+enum : int { kWdQ = 201, kWdKFull = 202, kWdVFull = 203, kWdKEmpty = 204, kWdVEmpty = 205, kWdSFull = 206,
+             kWdSFree = 207, kWdPFull = 208, kWdODone = 209, kWdAlign = 210 };
+
+struct Params {
+  int batch, heads, seq_q, seq_kv;
+  float scale_log2;      // scale * log2(e)
+  float keep_scale;      // 1/(1-p)
+  uint32_t thr, thr_h2;  // dropout threshold (see philox.cuh); thr_h2 = thr in both halves
+  int hcmp;              // thr <= 0x7C00: compare two fields with one packed FP16 compare
+  const int* kv_lengths;
+  uint32_t key[20];
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <bool DROP>
+__global__ void __launch_bounds__(NUM_THREADS, 2)
+attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                    const __grid_constant__ Params p, int* status) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if ((smem_u32(smem) & 1023u) != 0u) {
+    if (threadIdx.x == 0 && status != nullptr) *reinterpret_cast<volatile int*>(status) = kWdAlign;
+    return;
+  }
+  const uint32_t sQ = smem_u32(smem + OFF_Q), sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V),
+                 sP = smem_u32(smem + OFF_P);
+  const uint32_t bars = smem_u32(smem + OFF_BAR);
+  const uint32_t bar_q = bars;
+  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (1 + KV_STAGES + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (1 + 2 * KV_STAGES + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (1 + 3 * KV_STAGES + s); };
+  const uint32_t bar_s_full = bars + 8u * (1 + 4 * KV_STAGES);
+  const uint32_t bar_s_free = bar_s_full + 8u, bar_p_full = bar_s_full + 16u, bar_o_done = bar_s_full + 24u;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int q0 = blockIdx.x * BQ, h = blockIdx.y, b = blockIdx.z;
+  int kv_len = p.seq_kv;
+  if (p.kv_lengths != nullptr) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  const int nblk = (kv_len + BKV - 1) / BKV;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < KV_STAGES; ++s) {
+      mbar_init(k_full(s), 1); mbar_init(v_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
+    }
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_s_free, SOFTMAX_THREADS);
+    mbar_init(bar_p_full, SOFTMAX_THREADS);
+    mbar_init(bar_o_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (nblk > 0 && elect_one()) {
+      mbar_arrive_expect_tx(bar_q, TILE_BYTES);
+      tma_load_4d(sQ, &tmQ, bar_q, 0, q0, h, b);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag, status, kWdKEmpty)) break;
+        mbar_arrive_expect_tx(k_full(s), TILE_BYTES);
+        tma_load_4d(sK + s * TILE_BYTES, &tmK, k_full(s), 0, j * BKV, h, b);
+        if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag, status, kWdVEmpty)) break;
+        mbar_arrive_expect_tx(v_full(s), TILE_BYTES);
+        tma_load_4d(sV + s * TILE_BYTES, &tmV, v_full(s), 0, j * BKV, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (nblk > 0 && elect_one()) {
+      constexpr uint32_t IDESC_S = make_idesc_major(1u, 0u, 0u, 0u, BQ, BKV);   // Q, K: K-major
+      constexpr uint32_t IDESC_O = make_idesc_major(1u, 0u, 0u, 1u, BQ, HD);    // P K-major, V MN-major
+      const uint32_t tS = tmem_base, tO = tmem_base + 128;
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        if (!mbar_wait(k_full(s), ph, abort_flag, status, kWdKFull)) return false;
+        if (j > 0 && !mbar_wait(bar_s_free, (uint32_t)(j - 1) & 1u, abort_flag, status, kWdSFree)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          tc_mma_f16(tS, make_smem_desc(sQ + kk * 32, 16, 1024), make_smem_desc(sK + s * TILE_BYTES + kk * 32, 16, 1024),
+                     IDESC_S, kk != 0 ? 1u : 0u);
+        tc_commit(bar_s_full);
+        tc_commit(k_empty(s));
+        return true;
+      };
+      bool ok = mbar_wait(bar_q, 0u, abort_flag, status, kWdQ);
+      ok = ok && issue_s(0);
+      for (int j = 0; j < nblk && ok; ++j) {
+        if (j + 1 < nblk && !issue_s(j + 1)) break;
+        const int s = j % KV_STAGES;
+        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+        if (!mbar_wait(bar_p_full, (uint32_t)j & 1u, abort_flag, status, kWdPFull)) break;
+        if (!mbar_wait(v_full(s), ph, abort_flag, status, kWdVFull)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < BKV / 16; ++kk)
+          tc_mma_f16(tO, make_smem_desc(sP + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                     make_smem_desc(sV + s * TILE_BYTES + kk * 2048, TILE_BYTES, 1024), IDESC_O,
+                     (j | kk) != 0 ? 1u : 0u);
+        tc_commit(bar_o_done);
+        tc_commit(v_empty(s));
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------- softmax
+    const int qtr = warp & 3;                 // TMEM lane quarter this warp may touch
+    const int row = qtr * 32 + lane;          // tile row = TMEM lane
+    const uint32_t tS = tmem_base + (static_cast<uint32_t>(qtr * 32) << 16);
+    const uint32_t tO = tS + 128;
+    const float sl2 = p.scale_log2;
+    float m_run = -INFINITY, l_run = 0.0f;
+    // Philox block index of element (b, h, q0 + row, 0): eight keys per block
+    const unsigned long long blk_row =
+        ((((unsigned long long)b * p.heads + h) * p.seq_q + (unsigned long long)(q0 + row)) *
+         (unsigned long long)p.seq_kv) >> 3;
+    bool ok = true;
+    uint32_t r[2][32];
+    // the warp leaves a wait together, so the .aligned TMEM instructions stay convergent
+    auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) {
+      return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code)) != 0;
+    };
+    for (int j = 0; j < nblk && ok; ++j) {
+      if (!wait_warp(bar_s_full, (uint32_t)j & 1u, kWdSFull)) { ok = false; break; }
+      tc_fence_after();
+      const int valid = kv_len - j * BKV;     // columns of this block that are real keys
+      const bool tail = valid < BKV;
+      // pass 1: block maximum of the row
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+      tmem_ld_32x32(tS, r[0]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c < 3) tmem_ld_32x32(tS + (c + 1) * 32, r[(c + 1) & 1]);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = __uint_as_float(r[c & 1][i]), x1 = __uint_as_float(r[c & 1][i + 1]);
+          if (tail) {
+            if (c * 32 + i >= valid) x0 = -INFINITY;
+            if (c * 32 + i + 1 >= valid) x1 = -INFINITY;
+          }
+          mx0 = fmaxf(mx0, x0); mx1 = fmaxf(mx1, x1);
+        }
+      }
+      const float m_new = fmaxf(m_run, fmaxf(mx0, mx1) * sl2);
+      const float alpha = ex2_approx(m_run - m_new);     // 0 on the first block
+      // P and O are still in use by the previous block's second MMA
+      if (j > 0 && !wait_warp(bar_o_done, (uint32_t)(j - 1) & 1u, kWdODone)) { ok = false; break; }
+      tc_fence_after();
+      // pass 2: probabilities (unnormalised), their sum, dropout, FP16 tile P
+      uint64_t ls2 = pack2(0.0f, 0.0f);
+      const uint64_t sl2_2 = pack2(sl2, sl2), nm2 = pack2(-m_new, -m_new);
+      tmem_ld_32x32(tS, r[0]);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        tmem_ld_wait();
+        if (c < 3) tmem_ld_32x32(tS + (c + 1) * 32, r[(c + 1) & 1]);
+        else {
+          tc_fence_before();
+          mbar_arrive(bar_s_free);            // S may be overwritten by the next block's scores
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {         // 8 keys -> one 16-byte vector of P
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = g * 8 + 2 * k;
+            const float2 t = unpack2(fma2(pack2(__uint_as_float(r[c & 1][i]), __uint_as_float(r[c & 1][i + 1])), sl2_2, nm2));
+            float e0 = ex2_approx(t.x), e1 = ex2_approx(t.y);
+            if (tail) {
+              if (c * 32 + i >= valid) e0 = 0.0f;
+              if (c * 32 + i + 1 >= valid) e1 = 0.0f;
+            }
+            ls2 = add2(ls2, pack2(e0, e1));
+            const __half2 hh = __floats2half2_rn(e0, e1);
+            w[k] = *reinterpret_cast<const uint32_t*>(&hh);
+          }
+          if (DROP) {
+            uint32_t o[4];
+            const unsigned long long blk = blk_row + (unsigned)(j * (BKV / 8) + c * 4 + g);
+            philox_block((uint32_t)blk, (uint32_t)(blk >> 32), p.key, o);
+            if (p.hcmp) {
+              const __half2 thr2 = *reinterpret_cast<const __half2*>(&p.thr_h2);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t f = o[k] & 0x7FFF7FFFu;
+                w[k] &= __hgeu2_mask(*reinterpret_cast<const __half2*>(&f), thr2);
+              }
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                w[k] &= ((o[k] & 0x7FFFu) >= p.thr ? 0x0000FFFFu : 0u) |
+                        (((o[k] >> 16) & 0x7FFFu) >= p.thr ? 0xFFFF0000u : 0u);
+            }
+          }
+          const int col = c * 32 + g * 8;
+          const uint32_t addr = sP + (col >> 6) * TILE_BYTES + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+      }
+      const float2 ls = unpack2(ls2);
+      l_run = fmaf(l_run, alpha, ls.x + ls.y);
+      m_run = m_new;
+      // rescale the O row when the maximum of any row of this warp moved
+      if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
+        const uint64_t a2 = pack2(alpha, alpha);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          tmem_ld_32x32(tO + c * 32, r[0]);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float2 v = unpack2(mul2(pack2(__uint_as_float(r[0][i]), __uint_as_float(r[0][i + 1])), a2));
+            r[0][i] = __float_as_uint(v.x); r[0][i + 1] = __float_as_uint(v.y);
+          }
+          tmem_st_32x32(tO + c * 32, r[0]);
+        }
+        tmem_st_wait();
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(bar_p_full);
+    }
+    // ------------------------------------------------------------ final O row
+    if (ok && nblk > 0) ok = wait_warp(bar_o_done, (uint32_t)(nblk - 1) & 1u, kWdODone);
+    if (ok) {
+      tc_fence_after();
+      const float inv = nblk > 0 && l_run > 0.0f ? p.keep_scale / l_run : 0.0f;
+      const uint64_t inv2 = pack2(inv, inv);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        if (nblk > 0) { tmem_ld_32x32(tO + c * 32, r[0]); tmem_ld_wait(); }
+        else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[0][i] = 0u;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int i = g * 8 + 2 * k;
+            const float2 v = unpack2(mul2(pack2(__uint_as_float(r[0][i]), __uint_as_float(r[0][i + 1])), inv2));
+            const __half2 hh = __floats2half2_rn(v.x, v.y);
+            w[k] = *reinterpret_cast<const uint32_t*>(&hh);
+          }
+          // the Q tile is dead by now: it becomes the staging box of the output
+          const uint32_t addr = sQ + row * 128 + (((c * 4 + g) ^ (row & 7)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
+    if (threadIdx.x == 64 && !*abort_flag) {
+      tma_store_4d(&tmO, sQ, 0, q0, h, b);
+      bulk_commit_group();
+      bulk_wait_group0();
+    }
+  }
+
+  // ------------------------------------------------------------------ tear-down
+  __syncwarp();
+  if (*abort_flag) {
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace attn
+}  // namespace tfb

@@ -295,16 +295,45 @@ TensorFuseStatus tensorfuse_fused_softmax_dropout(const TensorFuseTensor* input,
                                           dropout_prob, seed, 0, stream));
 }
 
+// The reference validates and returns (src/tensorfuse_c_api.cpp:288-311); this
+// computes.  query/output [batch, seq_q, hidden], key/value [batch, seq_kv,
+// hidden] (src/tensorfuse/tensorfuse.h:95-98), heads split the hidden dimension,
+// scores scaled by 1/sqrt(hidden / heads), dropout on the attention weights
+// with a seed from the library's seed source.
 TensorFuseStatus tensorfuse_fused_multi_head_attention(const TensorFuseTensor* query,
                                                        const TensorFuseTensor* key,
                                                        const TensorFuseTensor* value,
                                                        TensorFuseTensor* output, int num_heads,
                                                        float dropout_prob, cudaStream_t stream) {
-  (void)dropout_prob; (void)stream;
   if (!Runtime::get().initialized()) return TENSORFUSE_ERROR_NOT_INITIALIZED;
   if (!query || !key || !value || !output) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
   if (num_heads <= 0) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
-  return TENSORFUSE_SUCCESS;
+  if (!(dropout_prob >= 0.0f && dropout_prob <= 1.0f)) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  const TensorFuseTensor* ts[4] = {query, key, value, output};
+  for (const TensorFuseTensor* t : ts) {
+    if (t->shape.ndims != 3) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
+    for (int i = 0; i < 3; ++i)
+      if (t->shape.dims[i] < 0) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
+  }
+  const int B = query->shape.dims[0], Sq = query->shape.dims[1], H = query->shape.dims[2];
+  const int Skv = key->shape.dims[1];
+  if (H % num_heads != 0) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
+  if (key->shape.dims[0] != B || value->shape.dims[0] != B || output->shape.dims[0] != B ||
+      key->shape.dims[2] != H || value->shape.dims[2] != H || output->shape.dims[2] != H ||
+      value->shape.dims[1] != Skv || output->shape.dims[1] != Sq)
+    return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
+  if (query->dtype != key->dtype || query->dtype != value->dtype || query->dtype != output->dtype)
+    return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  if (query->dtype != TENSORFUSE_FLOAT16 && query->dtype != TENSORFUSE_FLOAT32)
+    return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  if (B == 0 || Sq == 0 || H == 0) return TENSORFUSE_SUCCESS;
+  if (!query->data || !key->data || !value->data || !output->data) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  const unsigned long long seed = Runtime::get().next_seed();
+  t_last_seed = seed;
+  return tensorfuse_b200_attention(query->data, key->data, value->data, output->data, B, Sq, Skv, num_heads,
+                                   H / num_heads, H, H, H, H, 0, 0, 0, 0, 0, 0, 0, 0,
+                                   query->dtype == TENSORFUSE_FLOAT16 ? kF16 : kF32, 0.0f, dropout_prob, seed,
+                                   nullptr, stream);
 }
 
 TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseTensor* input,
@@ -405,6 +434,29 @@ TensorFuseStatus tensorfuse_b200_gemm_bias_act(const void* A, const void* B, con
   else if (activation == TENSORFUSE_ACTIVATION_NONE) epi = kEpiLinear;
   else return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
   return gemm_flat(A, B, bias, C, M, N, K, dtype, dtype, dtype, epi, alpha, beta, 1.0f, nullptr, nullptr, stream);
+}
+
+TensorFuseStatus tensorfuse_b200_attention(const void* q, const void* k, const void* v, void* out, int batch,
+                                         int seq_q, int seq_kv, int heads, int head_dim, long long ld_q,
+                                         long long ld_k, long long ld_v, long long ld_o, long long hs_q,
+                                         long long hs_k, long long hs_v, long long hs_o, long long bs_q,
+                                         long long bs_k, long long bs_v, long long bs_o, int dtype, float scale,
+                                         float dropout_prob, unsigned long long seed, const int* kv_lengths,
+                                         cudaStream_t stream) {
+  if (!q || !k || !v || !out) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  if (heads <= 0 || head_dim <= 0 || batch < 0 || seq_q < 0 || seq_kv < 0) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  AttnArgs a;
+  a.q = q; a.k = k; a.v = v; a.out = out;
+  a.batch = batch; a.seq_q = seq_q; a.seq_kv = seq_kv; a.heads = heads; a.head_dim = head_dim;
+  a.ld_q = ld_q; a.ld_k = ld_k; a.ld_v = ld_v; a.ld_o = ld_o;
+  // zero strides select the packed [batch, seq, heads * head_dim] arrangement of a row pitch
+  a.hs_q = hs_q ? hs_q : head_dim; a.hs_k = hs_k ? hs_k : head_dim;
+  a.hs_v = hs_v ? hs_v : head_dim; a.hs_o = hs_o ? hs_o : head_dim;
+  a.bs_q = bs_q ? bs_q : (long long)seq_q * ld_q; a.bs_k = bs_k ? bs_k : (long long)seq_kv * ld_k;
+  a.bs_v = bs_v ? bs_v : (long long)seq_kv * ld_v; a.bs_o = bs_o ? bs_o : (long long)seq_q * ld_o;
+  a.dtype = dtype; a.scale = scale; a.p = dropout_prob; a.seed = seed; a.kv_lengths = kv_lengths;
+  OwnerGuard og(out);
+  return to_status(launch_attention(a, stream));
 }
 
 void tensorfuse_b200_softmax_schedule(int row_len, int dtype, int aligned16, int* vec, int* warps) {

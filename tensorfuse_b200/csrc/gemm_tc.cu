@@ -12,28 +12,12 @@
 #include <mutex>
 
 #include "gemm_tc_kernel.cuh"
+#include "tma_host.h"
 
 namespace tfb {
 namespace {
 
 using namespace tc;
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      p = nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
 
 // 2-D row-major matrix [rows, cols] of 1-, 2- or 4-byte elements; box = 128
 // bytes of the contiguous dimension x box_rows rows, 128-byte swizzle, zero fill

@@ -69,6 +69,30 @@ LaunchResult launch_gemm_simt(const GemmArgs& a, cudaStream_t stream);
 // Picks the tensor-core kernel when eligible, else the CUDA-core kernel.
 LaunchResult launch_gemm(const GemmArgs& a, cudaStream_t stream);
 
+// ------------------------------------------------- multi-head attention
+// out[b, i, h, :] = sum_j keep(b,h,i,j)/(1-p) * softmax_j(scale * q[b,i,h,:].k[b,j,h,:]) * v[b,j,h,:]
+// Element (b, s, h, c) of a tensor sits at base + b*bs + s*ld + h*hs + c (in
+// elements); [batch, seq, hidden] is ld = hidden, hs = head_dim, bs = seq*hidden.
+// Keys j >= kv_lengths[b] (when given) are masked; a row with no valid key
+// yields zeros.  The dropout decision of probability (b, h, i, j) is that of
+// element ((b*heads + h)*seq_q + i)*seq_kv + j of a [B, H, Sq, Skv] tensor in
+// the softmax+dropout operator, so the fused result equals the composition
+// softmax_dropout(scores) . V for the same seed.
+struct AttnArgs {
+  const void* q; const void* k; const void* v; void* out;
+  int batch, seq_q, seq_kv, heads, head_dim;
+  long long ld_q, ld_k, ld_v, ld_o;   // between sequence positions
+  long long hs_q, hs_k, hs_v, hs_o;   // between heads
+  long long bs_q, bs_k, bs_v, bs_o;   // between batch items
+  int dtype;                          // kF16 | kF32
+  float scale;                        // <= 0 selects 1/sqrt(head_dim)
+  float p;
+  unsigned long long seed;
+  const int* kv_lengths;              // device pointer to `batch` ints, or null
+};
+bool attention_tc_eligible(const AttnArgs& a);
+LaunchResult launch_attention(const AttnArgs& a, cudaStream_t stream);
+
 // Device-side watchdog: 0 when no bounded wait has expired since the last
 // reset, else the code of the first wait that gave up.
 int watchdog_status();

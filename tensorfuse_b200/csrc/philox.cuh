@@ -1,0 +1,58 @@
+// philox.cuh -- Philox4x32-10 as the dropout generator of the library.
+//
+// Eight consecutive elements of a tensor share one Philox block: counter =
+// (global element index / 8, 0, 0) split into two 32-bit words, key = seed.
+// Element e of the block takes the 16-bit field (word e/2, half e%2) and is
+// kept when the low 15 bits of that field are >= round(p * 32768).  The
+// decision depends only on the element's position in the whole tensor, so it
+// does not change with the way rows are sharded across GPUs or tiled inside a
+// kernel.
+#pragma once
+#include <math.h>
+#include <stdint.h>
+
+namespace tfb {
+
+// Round keys (the key schedule is a pair of additive Weyl sequences).
+inline void philox_round_keys(unsigned long long seed, uint32_t (&key)[20]) {
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  for (int r = 0; r < 10; ++r) {
+    key[2 * r] = k0; key[2 * r + 1] = k1;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+}
+// Drop when the 15-bit field < threshold; 0 disables dropout.
+inline uint32_t dropout_threshold(float p) {
+  if (!(p > 0.0f)) return 0u;
+  const double t = floor((double)p * 32768.0 + 0.5);
+  return (uint32_t)(t > 32768.0 ? 32768.0 : t);
+}
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void philox_block(uint32_t c0, uint32_t c1, const uint32_t* key,
+                                             uint32_t (&o)[4]) {
+  uint32_t c2 = 0u, c3 = 0u;
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ key[2 * r];
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ key[2 * r + 1];
+    c1 = (uint32_t)p1;
+    c3 = (uint32_t)p0;
+    c0 = n0;
+    c2 = n2;
+  }
+  o[0] = c0; o[1] = c1; o[2] = c2; o[3] = c3;
+}
+// Keep decision of the single element `idx` (global element index).
+__device__ __forceinline__ bool philox_keep(unsigned long long idx, const uint32_t* key, uint32_t thr) {
+  uint32_t o[4];
+  philox_block((uint32_t)(idx >> 3), (uint32_t)(idx >> 35), key, o);
+  const uint32_t el = (uint32_t)(idx & 7ull);
+  const uint32_t word = (el >> 1) == 0 ? o[0] : (el >> 1) == 1 ? o[1] : (el >> 1) == 2 ? o[2] : o[3];
+  return ((word >> (16u * (el & 1u))) & 0x7FFFu) >= thr;
+}
+#endif
+
+}  // namespace tfb

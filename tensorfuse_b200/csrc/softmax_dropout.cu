@@ -32,6 +32,7 @@
 #include <math.h>
 
 #include "kernels.h"
+#include "philox.cuh"
 #include "ptx.cuh"
 
 namespace tfb {
@@ -123,23 +124,6 @@ __device__ __forceinline__ uint64_t exp_pair(float x0, float x1, const ExpCtx& c
     const float2 t = unpack2(fma2(pack2(x0, x1), c.log2e2, c.negc2));
     return exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f)));
   }
-}
-
-__device__ __forceinline__ void philox_block(uint32_t c0, uint32_t c1, const uint32_t* key,
-                                             uint32_t (&o)[4]) {
-  uint32_t c2 = 0u, c3 = 0u;
-#pragma unroll
-  for (int r = 0; r < 10; ++r) {
-    const uint64_t p0 = (uint64_t)0xD2511F53u * c0;
-    const uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
-    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ key[2 * r];
-    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ key[2 * r + 1];
-    c1 = (uint32_t)p1;
-    c3 = (uint32_t)p0;
-    c0 = n0;
-    c2 = n2;
-  }
-  o[0] = c0; o[1] = c1; o[2] = c2; o[3] = c3;
 }
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -539,16 +523,11 @@ LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* ma
   SmParams sp;
   sp.in = in; sp.out = out; sp.mask = mask; sp.rows = rows; sp.L = L;
   sp.keep_scale = p >= 1.0f ? 0.0f : 1.0f / (1.0f - p);
-  double t = floor((double)p * 32768.0 + 0.5);
-  sp.thr = p > 0.0f ? (uint32_t)(t > 32768.0 ? 32768.0 : t) : 0u;
+  sp.thr = dropout_threshold(p);
   sp.thr_h2 = (sp.thr & 0xFFFFu) * 0x00010001u;
   sp.hcmp = sp.thr <= 0x7C00u ? 1 : 0;
   sp.first_row = first_row;
-  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
-  for (int r = 0; r < 10; ++r) {
-    sp.key[2 * r] = k0; sp.key[2 * r + 1] = k1;
-    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
-  }
+  philox_round_keys(seed, sp.key);
   const bool drop = sp.thr != 0u;
   const uintptr_t bits = (uintptr_t)in | (uintptr_t)out | ((uintptr_t)mask << 1);
   const bool aligned16 = (bits & 15u) == 0;

@@ -106,7 +106,8 @@ def test_stubs_allocate_and_mangled_symbols(tf):
     t = Tensor(); s = Shape(); s.ndims = 2; s.dims[0] = 4; s.dims[1] = 8
     assert L.tensorfuse_allocate_tensor(byref(t), byref(s), 1, torch.cuda.current_device()) == 0
     assert t.data and t.size_bytes == 64 and t.is_contiguous
-    assert L.tensorfuse_fused_multi_head_attention(byref(t), byref(t), byref(t), byref(t), 4, 0.0, None) == 0
+    # 2-D tensors: the operator takes [batch, seq, hidden] (tests/test_attention_gpu.py covers the computation)
+    assert L.tensorfuse_fused_multi_head_attention(byref(t), byref(t), byref(t), byref(t), 4, 0.0, None) == 11
     assert L.tensorfuse_fused_multi_head_attention(byref(t), byref(t), byref(t), byref(t), 0, 0.0, None) == 1
     assert L.tensorfuse_free_tensor(byref(t)) == 0 and not t.data
     assert L.tensorfuse_free_tensor(byref(t)) == 1
