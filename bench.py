@@ -429,7 +429,7 @@ def side_workloads(tf, L, dev, peaks, args):
 
 def run_only(args):
     """One kernel, device-resident operands, a handful of launches: the command
-    profiler captures are taken from (`--only gemm_fp16|gemm_int8|softmax|softmax_p0`)."""
+    profiler captures are taken from (`--only gemm_fp16|gemm_int8|softmax|softmax_p0|attention|attention_p0`)."""
     import torch
     import tensorfuse_b200 as tf
     from tensorfuse_b200._lib import lib as L
@@ -451,6 +451,16 @@ def run_only(args):
         fn = lambda: L.tensorfuse_b200_gemm_int8(A.data_ptr(), B.data_ptr(), b.data_ptr(), C.data_ptr(), Mi, Ni, Ki,
                                                  1e-2, 1e-4, 1, 1, 1, sp)
         work, unit = 2.0 * Mi * Ni * Ki / 1e12, "TOPS"
+    elif args.only in ("attention", "attention_p0"):
+        Bq, Sq, Hh, hd = 32, 512, 16, 64           # BERT-large attention, 32 sequences
+        qkv = torch.randn((Bq, Sq, 3, Hh * hd), device=dev).half()
+        out = torch.empty((Bq, Sq, Hh * hd), dtype=torch.float16, device=dev)
+        ld = 3 * Hh * hd
+        pd = 0.0 if args.only == "attention_p0" else 0.1
+        fn = lambda: L.tensorfuse_b200_attention(qkv[:, :, 0].data_ptr(), qkv[:, :, 1].data_ptr(), qkv[:, :, 2].data_ptr(),
+                                                 out.data_ptr(), Bq, Sq, Sq, Hh, hd, ld, ld, ld, Hh * hd, 0, 0, 0, 0,
+                                                 0, 0, 0, 0, 1, 0.0, pd, 5, None, sp)
+        work, unit = 4.0 * Bq * Hh * Sq * Sq * hd / 1e12, "TFLOPS"
     else:
         rows, Lr = 32 * 16 * 512, 512
         x = (torch.randn((rows, Lr), device=dev) / 8).half(); o = torch.empty_like(x)
@@ -505,13 +515,13 @@ def run_encoder(args):
     steps, warm = max(1, min(args.steps, 10)), max(1, min(args.warmup, 3))
     with torch.no_grad():
         for i in range(warm):
-            be.encoder_forward(x, layers, cfg, seed=i)
+            be.encoder_forward(x, layers, cfg, seed=i, attention=args.attention)
         sync()
         launches0 = tf.launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(steps):
-            y = be.encoder_forward(x, layers, cfg, seed=100 + i)
+            y = be.encoder_forward(x, layers, cfg, seed=100 + i, attention=args.attention)
         e1.record()
         torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
@@ -530,8 +540,11 @@ def run_encoder(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": "bert_large_encoder_forward", "layers": 24, "hidden": 1024, "heads": 16, "ffn": 4096,
                    "global_batch": batch, "seq_len": seq, "parallelism": f"dp{world}_batch_sharded_replicated_weights",
-                   "fused_ops": "softmax+dropout p=0.1 (attention probabilities), FFN-up GEMM+bias+GELU, FFN-down GEMM+bias",
-                   "other_ops": "torch (cuBLAS projections and attention matmuls, layer norm)"},
+                   "attention": args.attention,
+                   "fused_ops": ("multi-head attention with dropout p=0.1 (one kernel)" if args.attention == "fused" else
+                                 "softmax+dropout p=0.1 on materialised scores") + ", FFN-up GEMM+bias+GELU, FFN-down GEMM+bias",
+                   "other_ops": "torch (cuBLAS projections" + ("" if args.attention == "fused" else ", attention matmuls") +
+                                ", layer norm)"},
         "effective_tflops": flop / (ms * 1e-3) / 1e12,
         "gpu_launches": int(tf.launch_count() - launches0)}), flush=True)
     return 0
@@ -541,8 +554,10 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="gemm_fp16", choices=["gemm_fp16", "bert_large"],
                     help="gemm_fp16 = the headline (default); bert_large = encoder forward, tokens/s")
-    ap.add_argument("--only", default=None, choices=["gemm_fp16", "gemm_int8", "softmax", "softmax_p0"],
+    ap.add_argument("--only", default=None, choices=["gemm_fp16", "gemm_int8", "softmax", "softmax_p0", "attention", "attention_p0"],
                     help="run a single kernel a few times (profiling aid)")
+    ap.add_argument("--attention", default="fused", choices=["fused", "unfused"],
+                    help="bert_large workload: one fused attention kernel, or softmax+dropout between two matmuls")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)

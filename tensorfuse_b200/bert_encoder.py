@@ -4,7 +4,10 @@ This is a *caller* of the hot path (the fifth benchmark configuration: BERT-larg
 24 layers, hidden 1024, 16 heads of 64, FFN 4096, FP16, random weights), not a
 model zoo: PyTorch does the projections, the attention matmuls and the layer
 norms; libtensorfuse.so does
-  * the attention probabilities: fused_softmax_dropout on [b, heads, S, S] scores,
+  * attention: fused_multi_head_attention straight on the fused QKV buffer (the
+    probabilities never reach memory), or, with attention="unfused", the
+    attention probabilities through fused_softmax_dropout on [b, heads, S, S]
+    scores between two torch matmuls,
   * FFN-up:   fused GEMM + bias + GELU,
   * FFN-down: fused GEMM + bias (activation NONE).
 The batch dimension is the sharding dimension: each GPU (one process per GPU)
@@ -58,17 +61,37 @@ def gemm_bias_act(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, activation:
     return out
 
 
+def layer_seed(seed: int, layer: int) -> int:
+    return (seed * 1000003 + layer * 131) & 0xFFFFFFFFFFFF
+
+
 def encoder_forward(x: torch.Tensor, layers, cfg: EncoderConfig, seed: int = 4, attn_chunk: int = 32,
-                    keep_masks: list | None = None) -> torch.Tensor:
+                    keep_masks: list | None = None, attention: str = "fused") -> torch.Tensor:
     """x: [batch, seq, hidden] on a CUDA device.  Dropout is applied to the
-    attention probabilities only (that is where the fused operator sits); with
-    ``keep_masks`` (a list) the per-layer dropout masks are appended to it."""
+    attention probabilities only (that is where the fused operators sit).  With
+    attention="unfused" and ``keep_masks`` (a list) the per-layer dropout masks
+    are appended to it; the fused operator drops the entries that
+    fused_softmax_dropout drops on a [batch, heads, S, S] tensor with the seed
+    ``layer_seed(seed, layer)``."""
     Bsz, S, H = x.shape
     nh, d = cfg.heads, H // cfg.heads
     scale = 1.0 / math.sqrt(d)
     h = x.reshape(Bsz * S, H).contiguous()
     for li, p in enumerate(layers):
-        qkv = torch.addmm(p["bqkv"], h, p["wqkv"]).view(Bsz, S, 3, nh, d)
+        qkv = torch.addmm(p["bqkv"], h, p["wqkv"])
+        if attention == "fused":
+            qkv3 = qkv.view(Bsz, S, 3, H)
+            ctx2 = torch.empty((Bsz, S, H), dtype=h.dtype, device=h.device)
+            tf.fused_multi_head_attention(qkv3[:, :, 0], qkv3[:, :, 1], qkv3[:, :, 2], ctx2, nh, cfg.dropout,
+                                          seed=layer_seed(seed, li))
+            ctx2 = ctx2.view(Bsz * S, H)
+            attn = torch.addmm(p["bo"], ctx2, p["wo"])
+            h = torch.nn.functional.layer_norm(h + attn, (H,), p["ln1_g"], p["ln1_b"], cfg.eps)
+            up = gemm_bias_act(h, p["w1"], p["b1"], "gelu")
+            down = gemm_bias_act(up, p["w2"], p["b2"], "none")
+            h = torch.nn.functional.layer_norm(h + down, (H,), p["ln2_g"], p["ln2_b"], cfg.eps)
+            continue
+        qkv = qkv.view(Bsz, S, 3, nh, d)
         q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))      # [B, nh, S, d]
         ctx = torch.empty((Bsz, nh, S, d), dtype=h.dtype, device=h.device)
         layer_masks = []
@@ -76,7 +99,7 @@ def encoder_forward(x: torch.Tensor, layers, cfg: EncoderConfig, seed: int = 4, 
             b1 = min(Bsz, b0 + attn_chunk)
             scores = torch.matmul(q[b0:b1], k[b0:b1].transpose(-1, -2)) * scale    # [b, nh, S, S]
             probs, mask = tf.fused_softmax_dropout(scores.contiguous(), dropout_prob=cfg.dropout,
-                                                   seed=(seed * 1000003 + li * 131 + b0) & 0xFFFFFFFFFFFF)
+                                                   seed=layer_seed(seed, li) + b0)
             if keep_masks is not None:
                 layer_masks.append(mask)
             ctx[b0:b1] = torch.matmul(probs, v[b0:b1])

@@ -22,7 +22,7 @@ def test_small_encoder_matches_fp32_reference(tf, dropout):
     x = torch.randn((5, 128, cfg.hidden), generator=g).to(dev, torch.float16)
     masks = []
     with torch.no_grad():
-        y = be.encoder_forward(x, layers, cfg, seed=7, attn_chunk=2, keep_masks=masks)
+        y = be.encoder_forward(x, layers, cfg, seed=7, attn_chunk=2, keep_masks=masks, attention="unfused")
         ref = be.reference_forward(x, layers, cfg, masks=masks if dropout > 0 else None)
     torch.cuda.synchronize()
     assert torch.isfinite(y).all()
@@ -31,5 +31,32 @@ def test_small_encoder_matches_fp32_reference(tf, dropout):
         assert abs(float(masks[0].float().mean()) - (1 - dropout)) < 0.01
     else:
         assert int(masks[0].min()) == 1
+    err = (y.float() - ref).abs().max().item()
+    assert err < 3e-2, err
+
+
+@pytest.mark.parametrize("dropout", [0.0, 0.1])
+def test_small_encoder_with_fused_attention(tf, dropout):
+    from tensorfuse_b200 import bert_encoder as be
+    cfg = be.EncoderConfig(layers=3, hidden=256, heads=4, ffn=1024, dropout=dropout)
+    dev = torch.device("cuda")
+    layers = be.random_weights(cfg, dev, seed=4)
+    for p in layers:
+        for k in ("wqkv", "wo", "w1", "w2"):
+            p[k].mul_(3.0)
+    g = torch.Generator(device="cpu"); g.manual_seed(0)
+    B, S = 5, 128
+    x = torch.randn((B, S, cfg.hidden), generator=g).to(dev, torch.float16)
+    with torch.no_grad():
+        y = be.encoder_forward(x, layers, cfg, seed=7)
+        # the decisions the fused operator makes are those of the softmax+dropout operator with the same seed
+        masks = None
+        if dropout > 0:
+            zeros = torch.zeros((B, cfg.heads, S, S), dtype=torch.float16, device=dev)
+            masks = [tf.fused_softmax_dropout(zeros, dropout_prob=dropout, seed=be.layer_seed(7, li))[1]
+                     for li in range(cfg.layers)]
+        ref = be.reference_forward(x, layers, cfg, masks=masks)
+    torch.cuda.synchronize()
+    assert tf.watchdog_status() == 0
     err = (y.float() - ref).abs().max().item()
     assert err < 3e-2, err
