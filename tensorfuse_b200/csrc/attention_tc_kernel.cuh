@@ -72,6 +72,13 @@ struct Params {
   uint32_t key[20];
 };
 
+struct TrueT { static constexpr bool value = true; };
+struct FalseT { static constexpr bool value = false; };
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -201,12 +208,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) {
       return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code)) != 0;
     };
-    for (int j = 0; j < nblk && ok; ++j) {
-      if (!wait_warp(bar_s_full, (uint32_t)j & 1u, kWdSFull)) { ok = false; break; }
-      tc_fence_after();
-      const int valid = kv_len - j * BKV;     // columns of this block that are real keys
-      const bool tail = valid < BKV;
-      // pass 1: block maximum of the row
+    // Pass 1: maximum of the 128 scores of the row.  TAIL: the block holds fewer
+    // than 128 real keys (columns >= valid are zero-filled, not scores).
+    auto pass1 = [&](auto tail_c, int valid) -> float {
+      constexpr bool TAIL = decltype(tail_c)::value;
       float mx0 = -INFINITY, mx1 = -INFINITY;
       tmem_ld_32x32(tS, r[0]);
 #pragma unroll
@@ -214,23 +219,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tmem_ld_wait();
         if (c < 3) tmem_ld_32x32(tS + (c + 1) * 32, r[(c + 1) & 1]);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float x0 = __uint_as_float(r[c & 1][i]), x1 = __uint_as_float(r[c & 1][i + 1]);
-          if (tail) {
-            if (c * 32 + i >= valid) x0 = -INFINITY;
-            if (c * 32 + i + 1 >= valid) x1 = -INFINITY;
+        for (int i = 0; i < 32; i += 4) {
+          float x[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            x[u] = __uint_as_float(r[c & 1][i + u]);
+            if (TAIL && c * 32 + i + u >= valid) x[u] = -INFINITY;
           }
-          mx0 = fmaxf(mx0, x0); mx1 = fmaxf(mx1, x1);
+          mx0 = max3(mx0, x[0], x[1]);
+          mx1 = max3(mx1, x[2], x[3]);
         }
       }
-      const float m_new = fmaxf(m_run, fmaxf(mx0, mx1) * sl2);
-      const float alpha = ex2_approx(m_run - m_new);     // 0 on the first block
-      // P and O are still in use by the previous block's second MMA
-      if (j > 0 && !wait_warp(bar_o_done, (uint32_t)(j - 1) & 1u, kWdODone)) { ok = false; break; }
-      tc_fence_after();
-      // pass 2: probabilities (unnormalised), their sum, dropout, FP16 tile P
-      uint64_t ls2 = pack2(0.0f, 0.0f);
-      const uint64_t sl2_2 = pack2(sl2, sl2), nm2 = pack2(-m_new, -m_new);
+      return fmaxf(mx0, mx1);
+    };
+    // Pass 2: unnormalised probabilities 2^(s*scale*log2e - m), their FP32 sum,
+    // dropout, FP16 tile P (K-major, 128-byte swizzle).  Returns the row sum.
+    auto pass2 = [&](auto tail_c, int valid, int j, float m_new) -> float {
+      constexpr bool TAIL = decltype(tail_c)::value;
+      float ls0 = 0.0f, ls1 = 0.0f;
+      const float nm = -m_new;
       tmem_ld_32x32(tS, r[0]);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -246,13 +253,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int i = g * 8 + 2 * k;
-            const float2 t = unpack2(fma2(pack2(__uint_as_float(r[c & 1][i]), __uint_as_float(r[c & 1][i + 1])), sl2_2, nm2));
-            float e0 = ex2_approx(t.x), e1 = ex2_approx(t.y);
-            if (tail) {
+            float e0 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i]), sl2, nm));
+            float e1 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i + 1]), sl2, nm));
+            if (TAIL) {
               if (c * 32 + i >= valid) e0 = 0.0f;
               if (c * 32 + i + 1 >= valid) e1 = 0.0f;
             }
-            ls2 = add2(ls2, pack2(e0, e1));
+            ls0 += e0; ls1 += e1;
             const __half2 hh = __floats2half2_rn(e0, e1);
             w[k] = *reinterpret_cast<const uint32_t*>(&hh);
           }
@@ -280,8 +287,21 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                        : "memory");
         }
       }
-      const float2 ls = unpack2(ls2);
-      l_run = fmaf(l_run, alpha, ls.x + ls.y);
+      return ls0 + ls1;
+    };
+    for (int j = 0; j < nblk && ok; ++j) {
+      if (!wait_warp(bar_s_full, (uint32_t)j & 1u, kWdSFull)) { ok = false; break; }
+      tc_fence_after();
+      const int valid = kv_len - j * BKV;     // columns of this block that are real keys
+      const bool tail = valid < BKV;
+      const float mx = tail ? pass1(TrueT{}, valid) : pass1(FalseT{}, valid);
+      const float m_new = fmaxf(m_run, mx * sl2);
+      const float alpha = ex2_approx(m_run - m_new);     // 0 on the first block
+      // P and O are still in use by the previous block's second MMA
+      if (j > 0 && !wait_warp(bar_o_done, (uint32_t)(j - 1) & 1u, kWdODone)) { ok = false; break; }
+      tc_fence_after();
+      const float ls = tail ? pass2(TrueT{}, valid, j, m_new) : pass2(FalseT{}, valid, j, m_new);
+      l_run = fmaf(l_run, alpha, ls);
       m_run = m_new;
       // rescale the O row when the maximum of any row of this warp moved
       if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
