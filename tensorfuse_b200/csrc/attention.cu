@@ -199,7 +199,14 @@ LaunchResult run_tc(const AttnArgs& a, float scale, cudaStream_t stream) {
   p.hcmp = p.thr <= 0x7C00u ? 1 : 0;
   p.kv_lengths = a.kv_lengths;
   philox_round_keys(a.seed, p.key);
-  const dim3 grid((unsigned)((a.seq_q + BQ - 1) / BQ), (unsigned)a.heads, (unsigned)a.batch);
+  p.q_tiles = (a.seq_q + BQ - 1) / BQ;
+  const long long items = (long long)p.q_tiles * a.heads * a.batch;
+  if (items > 0x7FFFFFFFll) return kUnsupported;
+  p.n_tiles = (int)items;
+  int sms = 0;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (sms <= 0) sms = 148;
+  const unsigned grid = (unsigned)(items < 2ll * sms ? items : 2ll * sms);
   kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(mq, mk, mv, mo, p, watchdog_word());
   count_launch();
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
@@ -209,7 +216,6 @@ LaunchResult run_tc(const AttnArgs& a, float scale, cudaStream_t stream) {
 
 bool attention_tc_eligible(const AttnArgs& a) {
   if (a.dtype != kF16 || a.head_dim != attn::HD) return false;
-  if (a.batch > 65535 || a.heads > 65535) return false;
   const uintptr_t ptrs = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out;
   if (ptrs & 15u) return false;
   const long long strides[12] = {a.ld_q, a.ld_k, a.ld_v, a.ld_o, a.hs_q, a.hs_k, a.hs_v, a.hs_o,

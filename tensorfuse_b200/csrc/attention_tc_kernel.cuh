@@ -4,9 +4,13 @@
 // The probabilities never reach device memory.  (The reference declares this
 // operator and leaves it empty: reference src/tensorfuse_c_api.cpp:288-311.)
 //
-// One CTA owns 128 query rows of one head and walks the keys in blocks of 128;
-// two CTAs fit on an SM (112 KB of shared memory, 256 TMEM columns each), so one
-// CTA's softmax arithmetic overlaps the other's tensor-core work.
+// A work item is 128 query rows of one head; its keys are walked in blocks of
+// 128.  The kernel is persistent: two CTAs per SM (112 KB of shared memory, 256
+// TMEM columns each) take work items round-robin, so TMEM allocation, barrier
+// set-up and descriptor fetches happen once, the next item's Q, K, V arrive and
+// its first scores are computed while the current item's output rows are
+// normalised and stored, and one CTA's softmax arithmetic overlaps the other's
+// tensor-core work.
 //   warp 0, one lane : TMA producer.  Q once; K and V blocks into a 2-deep ring
 //                      of 128-byte-swizzled boxes (4-D tensor maps: any batch /
 //                      sequence / head strides, zero fill past the sequence end).
@@ -24,7 +28,8 @@
 //                      running maximum moves, the same thread rescales its O row
 //                      in TMEM (tcgen05.ld / st) before releasing P to the MMA
 //                      issuer.  The final O row is divided by the row sum, scaled
-//                      by 1/(1-p), converted and stored through TMA.
+//                      by 1/(1-p), converted, staged in the (then idle) P tile and
+//                      stored through TMA.
 // Every mbarrier wait is bounded (ptx.cuh): an expired wait raises the CTA abort
 // flag, records a code in the watchdog word, and all roles fall through to the
 // tear-down that frees TMEM.
@@ -52,18 +57,19 @@ constexpr int OFF_K = OFF_Q + TILE_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * TILE_BYTES;
 constexpr int OFF_P = OFF_V + KV_STAGES * TILE_BYTES;   // two boxes: keys 0..63, 64..127
 constexpr int OFF_BAR = OFF_P + 2 * TILE_BYTES;
-// barriers: q, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_free, p_full, o_done
-constexpr int NUM_BARS = 1 + 4 * KV_STAGES + 4;
+// barriers: q_full, q_empty, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_free, p_full, o_done
+constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 5;   // + the softmax warps' own rendezvous
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16;
 static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs per SM");
 
 // watchdog codes of this kernel
 enum : int { kWdQ = 201, kWdKFull = 202, kWdVFull = 203, kWdKEmpty = 204, kWdVEmpty = 205, kWdSFull = 206,
-             kWdSFree = 207, kWdPFull = 208, kWdODone = 209, kWdAlign = 210 };
+             kWdSFree = 207, kWdPFull = 208, kWdODone = 209, kWdAlign = 210, kWdSync = 211 };
 
 struct Params {
   int batch, heads, seq_q, seq_kv;
+  int q_tiles, n_tiles;  // query tiles per (batch item, head); work items in all
   float scale_log2;      // scale * log2(e)
   float keep_scale;      // 1/(1-p)
   uint32_t thr, thr_h2;  // dropout threshold (see philox.cuh); thr_h2 = thr in both halves
@@ -98,24 +104,33 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t sQ = smem_u32(smem + OFF_Q), sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V),
                  sP = smem_u32(smem + OFF_P);
   const uint32_t bars = smem_u32(smem + OFF_BAR);
-  const uint32_t bar_q = bars;
-  auto k_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto v_full = [&](int s) { return bars + 8u * (1 + KV_STAGES + s); };
-  auto k_empty = [&](int s) { return bars + 8u * (1 + 2 * KV_STAGES + s); };
-  auto v_empty = [&](int s) { return bars + 8u * (1 + 3 * KV_STAGES + s); };
-  const uint32_t bar_s_full = bars + 8u * (1 + 4 * KV_STAGES);
+  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8u;
+  auto k_full = [&](int s) { return bars + 8u * (2 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (2 + KV_STAGES + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (2 + 2 * KV_STAGES + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (2 + 3 * KV_STAGES + s); };
+  const uint32_t bar_s_full = bars + 8u * (2 + 4 * KV_STAGES);
   const uint32_t bar_s_free = bar_s_full + 8u, bar_p_full = bar_s_full + 16u, bar_o_done = bar_s_full + 24u;
+  const uint32_t bar_sm_sync = bar_s_full + 32u;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * BQ, h = blockIdx.y, b = blockIdx.z;
-  int kv_len = p.seq_kv;
-  if (p.kv_lengths != nullptr) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
-  const int nblk = (kv_len + BKV - 1) / BKV;
+  // Work item t -> (query tile, head, batch item); the query tile runs fastest so
+  // that CTAs working side by side read the same K and V from L2.
+  auto tile_coords = [&](int t, int& q0, int& h, int& b, int& kv_len) {
+    const int qt = t % p.q_tiles;
+    const int rest = t / p.q_tiles;
+    h = rest % p.heads;
+    b = rest / p.heads;
+    q0 = qt * BQ;
+    kv_len = p.seq_kv;
+    if (p.kv_lengths != nullptr) kv_len = max(0, min(kv_len, p.kv_lengths[b]));
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_q, 1);
+    mbar_init(bar_q_full, 1);
+    mbar_init(bar_q_empty, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full(s), 1); mbar_init(v_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
     }
@@ -123,6 +138,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(bar_s_free, SOFTMAX_THREADS);
     mbar_init(bar_p_full, SOFTMAX_THREADS);
     mbar_init(bar_o_done, 1);
+    mbar_init(bar_sm_sync, SOFTMAX_THREADS);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
@@ -136,33 +152,47 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Counters that run across the work items of this CTA: `wt` counts items with
+  // at least one key block (phases of the Q barriers), `g` counts key blocks
+  // (ring stage and phases of the per-block barriers).
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (nblk > 0 && elect_one()) {
-      mbar_arrive_expect_tx(bar_q, TILE_BYTES);
-      tma_load_4d(sQ, &tmQ, bar_q, 0, q0, h, b);
-      for (int j = 0; j < nblk; ++j) {
-        const int s = j % KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag, status, kWdKEmpty)) break;
-        mbar_arrive_expect_tx(k_full(s), TILE_BYTES);
-        tma_load_4d(sK + s * TILE_BYTES, &tmK, k_full(s), 0, j * BKV, h, b);
-        if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag, status, kWdVEmpty)) break;
-        mbar_arrive_expect_tx(v_full(s), TILE_BYTES);
-        tma_load_4d(sV + s * TILE_BYTES, &tmV, v_full(s), 0, j * BKV, h, b);
+    if (elect_one()) {
+      uint32_t wt = 0, g = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+        int q0, h, b, kv_len;
+        tile_coords(t, q0, h, b, kv_len);
+        const int nblk = (kv_len + BKV - 1) / BKV;
+        if (nblk == 0) continue;
+        if (!mbar_wait(bar_q_empty, (wt & 1u) ^ 1u, abort_flag, status, kWdQ)) break;
+        mbar_arrive_expect_tx(bar_q_full, TILE_BYTES);
+        tma_load_4d(sQ, &tmQ, bar_q_full, 0, q0, h, b);
+        ++wt;
+        for (int j = 0; j < nblk; ++j, ++g) {
+          const int s = g % KV_STAGES;
+          const uint32_t ph = (g / KV_STAGES) & 1u;
+          if (!mbar_wait(k_empty(s), ph ^ 1u, abort_flag, status, kWdKEmpty)) { ok = false; break; }
+          mbar_arrive_expect_tx(k_full(s), TILE_BYTES);
+          tma_load_4d(sK + s * TILE_BYTES, &tmK, k_full(s), 0, j * BKV, h, b);
+          if (!mbar_wait(v_empty(s), ph ^ 1u, abort_flag, status, kWdVEmpty)) { ok = false; break; }
+          mbar_arrive_expect_tx(v_full(s), TILE_BYTES);
+          tma_load_4d(sV + s * TILE_BYTES, &tmV, v_full(s), 0, j * BKV, h, b);
+        }
       }
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (nblk > 0 && elect_one()) {
+    if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc_major(1u, 0u, 0u, 0u, BQ, BKV);   // Q, K: K-major
       constexpr uint32_t IDESC_O = make_idesc_major(1u, 0u, 0u, 1u, BQ, HD);    // P K-major, V MN-major
       const uint32_t tS = tmem_base, tO = tmem_base + 128;
-      auto issue_s = [&](int j) -> bool {
-        const int s = j % KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
+      // S = Q K^T of key block number gi (counted over the whole CTA)
+      auto issue_s = [&](uint32_t gi, bool last_of_item) -> bool {
+        const int s = gi % KV_STAGES;
+        const uint32_t ph = (gi / KV_STAGES) & 1u;
         if (!mbar_wait(k_full(s), ph, abort_flag, status, kWdKFull)) return false;
-        if (j > 0 && !mbar_wait(bar_s_free, (uint32_t)(j - 1) & 1u, abort_flag, status, kWdSFree)) return false;
+        if (gi > 0 && !mbar_wait(bar_s_free, (gi - 1) & 1u, abort_flag, status, kWdSFree)) return false;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
@@ -170,24 +200,56 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                      IDESC_S, kk != 0 ? 1u : 0u);
         tc_commit(bar_s_full);
         tc_commit(k_empty(s));
+        if (last_of_item) tc_commit(bar_q_empty);     // Q may be replaced by the next item's rows
         return true;
       };
-      bool ok = mbar_wait(bar_q, 0u, abort_flag, status, kWdQ);
-      ok = ok && issue_s(0);
-      for (int j = 0; j < nblk && ok; ++j) {
-        if (j + 1 < nblk && !issue_s(j + 1)) break;
-        const int s = j % KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / KV_STAGES) & 1u;
-        if (!mbar_wait(bar_p_full, (uint32_t)j & 1u, abort_flag, status, kWdPFull)) break;
-        if (!mbar_wait(v_full(s), ph, abort_flag, status, kWdVFull)) break;
-        tc_fence_after();
+      uint32_t wt = 0, g = 0;
+      bool ok = true;
+      // first scores of the first item with work
+      int t = blockIdx.x, nblk = 0;
+      auto next_item = [&]() {        // advance t to the next item that has key blocks; sets nblk
+        for (; t < p.n_tiles; t += gridDim.x) {
+          int q0, h, b, kv_len;
+          tile_coords(t, q0, h, b, kv_len);
+          nblk = (kv_len + BKV - 1) / BKV;
+          if (nblk > 0) return true;
+        }
+        return false;
+      };
+      bool have = next_item();
+      if (have) {
+        ok = mbar_wait(bar_q_full, wt & 1u, abort_flag, status, kWdQ);
+        ++wt;
+        ok = ok && issue_s(g, nblk == 1);
+      }
+      while (have && ok) {
+        const int nb = nblk;
+        for (int j = 0; j < nb && ok; ++j, ++g) {
+          if (j + 1 < nb) {
+            if (!issue_s(g + 1, j + 2 == nb)) { ok = false; break; }
+          } else {
+            // the scores of the next item's first block go out before this item's last P V
+            t += gridDim.x;
+            have = next_item();
+            if (have) {
+              if (!mbar_wait(bar_q_full, wt & 1u, abort_flag, status, kWdQ)) { ok = false; break; }
+              ++wt;
+              if (!issue_s(g + 1, nblk == 1)) { ok = false; break; }
+            }
+          }
+          const int s = g % KV_STAGES;
+          const uint32_t ph = (g / KV_STAGES) & 1u;
+          if (!mbar_wait(bar_p_full, g & 1u, abort_flag, status, kWdPFull)) { ok = false; break; }
+          if (!mbar_wait(v_full(s), ph, abort_flag, status, kWdVFull)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int kk = 0; kk < BKV / 16; ++kk)
-          tc_mma_f16(tO, make_smem_desc(sP + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                     make_smem_desc(sV + s * TILE_BYTES + kk * 2048, TILE_BYTES, 1024), IDESC_O,
-                     (j | kk) != 0 ? 1u : 0u);
-        tc_commit(bar_o_done);
-        tc_commit(v_empty(s));
+          for (int kk = 0; kk < BKV / 16; ++kk)
+            tc_mma_f16(tO, make_smem_desc(sP + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 16, 1024),
+                       make_smem_desc(sV + s * TILE_BYTES + kk * 2048, TILE_BYTES, 1024), IDESC_O,
+                       (j | kk) != 0 ? 1u : 0u);
+          tc_commit(bar_o_done);
+          tc_commit(v_empty(s));
+        }
       }
     }
   } else {
@@ -197,16 +259,32 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const uint32_t tS = tmem_base + (static_cast<uint32_t>(qtr * 32) << 16);
     const uint32_t tO = tS + 128;
     const float sl2 = p.scale_log2;
-    float m_run = -INFINITY, l_run = 0.0f;
-    // Philox block index of element (b, h, q0 + row, 0): eight keys per block
-    const unsigned long long blk_row =
-        ((((unsigned long long)b * p.heads + h) * p.seq_q + (unsigned long long)(q0 + row)) *
-         (unsigned long long)p.seq_kv) >> 3;
     bool ok = true;
+    bool store_pending = false;               // a TMA store may still be reading the staging box (P box 0)
+    uint32_t g = 0;                           // key blocks processed by this CTA so far
     uint32_t r[2][32];
+    unsigned long long blk_row = 0;           // Philox block index of element (b, h, q0 + row, 0)
     // the warp leaves a wait together, so the .aligned TMEM instructions stay convergent
     auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) {
       return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code)) != 0;
+    };
+    // Rendezvous of the four softmax warps on an mbarrier, bounded like every
+    // other wait (a named barrier would hang the CTA if one warp had given up).
+    uint32_t sync_phase = 0;
+    auto softmax_sync = [&]() {
+      mbar_arrive(bar_sm_sync);
+      const bool w = wait_warp(bar_sm_sync, sync_phase, kWdSync);
+      sync_phase ^= 1u;
+      return w;
+    };
+    // the staging box is written again only after the previous store has read it
+    auto staging_ready = [&]() {
+      if (store_pending) {
+        if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        store_pending = false;
+        return softmax_sync();
+      }
+      return true;
     };
     // Pass 1: maximum of the 128 scores of the row.  TAIL: the block holds fewer
     // than 128 real keys (columns >= valid are zero-filled, not scores).
@@ -248,11 +326,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           mbar_arrive(bar_s_free);            // S may be overwritten by the next block's scores
         }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {         // 8 keys -> one 16-byte vector of P
+        for (int gq = 0; gq < 4; ++gq) {      // 8 keys -> one 16-byte vector of P
           uint32_t w[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const int i = g * 8 + 2 * k;
+            const int i = gq * 8 + 2 * k;
             float e0 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i]), sl2, nm));
             float e1 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i + 1]), sl2, nm));
             if (TAIL) {
@@ -265,7 +343,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           if (DROP) {
             uint32_t o[4];
-            const unsigned long long blk = blk_row + (unsigned)(j * (BKV / 8) + c * 4 + g);
+            const unsigned long long blk = blk_row + (unsigned)(j * (BKV / 8) + c * 4 + gq);
             philox_block((uint32_t)blk, (uint32_t)(blk >> 32), p.key, o);
             if (p.hcmp) {
               const __half2 thr2 = *reinterpret_cast<const __half2*>(&p.thr_h2);
@@ -281,7 +359,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         (((o[k] >> 16) & 0x7FFFu) >= p.thr ? 0xFFFF0000u : 0u);
             }
           }
-          const int col = c * 32 + g * 8;
+          const int col = c * 32 + gq * 8;
           const uint32_t addr = sP + (col >> 6) * TILE_BYTES + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                        : "memory");
@@ -289,46 +367,51 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       return ls0 + ls1;
     };
-    for (int j = 0; j < nblk && ok; ++j) {
-      if (!wait_warp(bar_s_full, (uint32_t)j & 1u, kWdSFull)) { ok = false; break; }
-      tc_fence_after();
-      const int valid = kv_len - j * BKV;     // columns of this block that are real keys
-      const bool tail = valid < BKV;
-      const float mx = tail ? pass1(TrueT{}, valid) : pass1(FalseT{}, valid);
-      const float m_new = fmaxf(m_run, mx * sl2);
-      const float alpha = ex2_approx(m_run - m_new);     // 0 on the first block
-      // P and O are still in use by the previous block's second MMA
-      if (j > 0 && !wait_warp(bar_o_done, (uint32_t)(j - 1) & 1u, kWdODone)) { ok = false; break; }
-      tc_fence_after();
-      const float ls = tail ? pass2(TrueT{}, valid, j, m_new) : pass2(FalseT{}, valid, j, m_new);
-      l_run = fmaf(l_run, alpha, ls);
-      m_run = m_new;
-      // rescale the O row when the maximum of any row of this warp moved
-      if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
-        const uint64_t a2 = pack2(alpha, alpha);
+
+    for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
+      int q0, h, b, kv_len;
+      tile_coords(t, q0, h, b, kv_len);
+      const int nblk = (kv_len + BKV - 1) / BKV;
+      blk_row = ((((unsigned long long)b * p.heads + h) * p.seq_q + (unsigned long long)(q0 + row)) *
+                 (unsigned long long)p.seq_kv) >> 3;
+      float m_run = -INFINITY, l_run = 0.0f;
+      for (int j = 0; j < nblk && ok; ++j, ++g) {
+        if (!wait_warp(bar_s_full, g & 1u, kWdSFull)) { ok = false; break; }
+        tc_fence_after();
+        const int valid = kv_len - j * BKV;     // columns of this block that are real keys
+        const bool tail = valid < BKV;
+        const float mx = tail ? pass1(TrueT{}, valid) : pass1(FalseT{}, valid);
+        const float m_new = fmaxf(m_run, mx * sl2);
+        const float alpha = ex2_approx(m_run - m_new);     // 0 on the first block
+        // P and O are still in use by the previous block's second MMA
+        if (j > 0 && !wait_warp(bar_o_done, (g - 1) & 1u, kWdODone)) { ok = false; break; }
+        if (j == 0 && !staging_ready()) { ok = false; break; }
+        tc_fence_after();
+        const float ls = tail ? pass2(TrueT{}, valid, j, m_new) : pass2(FalseT{}, valid, j, m_new);
+        l_run = fmaf(l_run, alpha, ls);
+        m_run = m_new;
+        // rescale the O row when the maximum of any row of this warp moved
+        if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          tmem_ld_32x32(tO + c * 32, r[0]);
-          tmem_ld_wait();
+          for (int c = 0; c < 2; ++c) {
+            tmem_ld_32x32(tO + c * 32, r[0]);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float2 v = unpack2(mul2(pack2(__uint_as_float(r[0][i]), __uint_as_float(r[0][i + 1])), a2));
-            r[0][i] = __float_as_uint(v.x); r[0][i + 1] = __float_as_uint(v.y);
+            for (int i = 0; i < 32; ++i) r[0][i] = __float_as_uint(__uint_as_float(r[0][i]) * alpha);
+            tmem_st_32x32(tO + c * 32, r[0]);
           }
-          tmem_st_32x32(tO + c * 32, r[0]);
+          tmem_st_wait();
         }
-        tmem_st_wait();
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(bar_p_full);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(bar_p_full);
-    }
-    // ------------------------------------------------------------ final O row
-    if (ok && nblk > 0) ok = wait_warp(bar_o_done, (uint32_t)(nblk - 1) & 1u, kWdODone);
-    if (ok) {
+      // ---------------------------------------------------------- final O rows
+      if (ok && nblk > 0) ok = wait_warp(bar_o_done, (g - 1) & 1u, kWdODone);
+      if (!ok) break;
       tc_fence_after();
+      if (nblk == 0 && !staging_ready()) break;
       const float inv = nblk > 0 && l_run > 0.0f ? p.keep_scale / l_run : 0.0f;
-      const uint64_t inv2 = pack2(inv, inv);
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         if (nblk > 0) { tmem_ld_32x32(tO + c * 32, r[0]); tmem_ld_wait(); }
@@ -337,29 +420,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int i = 0; i < 32; ++i) r[0][i] = 0u;
         }
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
+        for (int gq = 0; gq < 4; ++gq) {
           uint32_t w[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const int i = g * 8 + 2 * k;
-            const float2 v = unpack2(mul2(pack2(__uint_as_float(r[0][i]), __uint_as_float(r[0][i + 1])), inv2));
-            const __half2 hh = __floats2half2_rn(v.x, v.y);
+            const int i = gq * 8 + 2 * k;
+            const __half2 hh = __floats2half2_rn(__uint_as_float(r[0][i]) * inv, __uint_as_float(r[0][i + 1]) * inv);
             w[k] = *reinterpret_cast<const uint32_t*>(&hh);
           }
-          // the Q tile is dead by now: it becomes the staging box of the output
-          const uint32_t addr = sQ + row * 128 + (((c * 4 + g) ^ (row & 7)) << 4);
+          // P box 0 is free once the item's last P V has completed: it stages the output rows
+          const uint32_t addr = sP + row * 128 + (((c * 4 + gq) ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                        : "memory");
         }
       }
       fence_proxy_async_smem();
+      tc_fence_before();                       // the O reads above precede the next item's first P V
+      if (!softmax_sync()) break;
+      if (threadIdx.x == 64) {
+        tma_store_4d(&tmO, sP, 0, q0, h, b);
+        bulk_commit_group();
+      }
+      store_pending = true;
     }
-    asm volatile("bar.sync 1, %0;" ::"n"(SOFTMAX_THREADS) : "memory");
-    if (threadIdx.x == 64 && !*abort_flag) {
-      tma_store_4d(&tmO, sQ, 0, q0, h, b);
-      bulk_commit_group();
-      bulk_wait_group0();
-    }
+    if (threadIdx.x == 64) bulk_wait_group0();
   }
 
   // ------------------------------------------------------------------ tear-down
