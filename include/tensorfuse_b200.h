@@ -108,6 +108,24 @@ TensorFuseStatus tensorfuse_b200_attention(const void* q, const void* k, const v
                                            float scale, float dropout_prob, unsigned long long seed,
                                            const int* kv_lengths, cudaStream_t stream);
 
+/* Per-tensor symmetric INT8 quantisation of n FP16 / FP32 elements on the
+ * device: *scale_dev = max|x| / 127 (1 for an all-zero tensor), q[i] =
+ * clip(rint(x[i] / scale), -127, 127).  The scale stays in device memory, which
+ * is where TensorFuseTensor.scale of the INT8 GEMM expects it.  (The reference
+ * has no quantiser; its Python binding guesses scales from the INT8 data on the
+ * host, src/python/core_bindings.cpp:467-491.)  Asynchronous, allocates nothing. */
+TensorFuseStatus tensorfuse_b200_quantize_int8(const void* x, int dtype, long long n, signed char* q,
+                                               float* scale_dev, cudaStream_t stream);
+
+/* out = LayerNorm(x + residual) * gamma + beta over rows of `hidden` elements,
+ * FP16 or FP32 storage, FP32 arithmetic (residual may be NULL).  The glue
+ * between the fused operators inside tensorfuse_fused_transformer_layer; the
+ * reference carries layer-norm weights in TensorFuseTransformerParams
+ * (src/tensorfuse/types.h:153-185) but has no kernel for them. */
+TensorFuseStatus tensorfuse_b200_add_layernorm(const void* x, const void* residual, const void* gamma,
+                                               const void* beta, void* out, long long rows, int hidden,
+                                               int dtype, float eps, cudaStream_t stream);
+
 /* Row-sharded softmax+dropout: `rows` rows of length `row_len`; `first_row`
  * is the index of the first of them inside the whole tensor, so that a shard
  * draws exactly the dropout decisions it would get as part of the whole.

@@ -191,6 +191,50 @@ def attention(q, k, v, heads, p=0.0, seed=0, scale=None, kv_lengths=None, thread
     return out
 
 
+def add_layernorm(x, residual, gamma, beta, eps):
+    """LayerNorm(x + residual) * gamma + beta over the last axis in float64
+    (biased variance).  The reference carries the weights and epsilon for this in
+    TensorFuseTransformerParams (src/tensorfuse/types.h:153-185) and computes
+    nothing with them; this is the textbook definition."""
+    s = np.asarray(x, np.float64) + (0.0 if residual is None else np.asarray(residual, np.float64))
+    mean = s.mean(axis=-1, keepdims=True)
+    var = ((s - mean) ** 2).mean(axis=-1, keepdims=True)
+    return (s - mean) / np.sqrt(var + eps) * np.asarray(gamma, np.float64) + np.asarray(beta, np.float64)
+
+
+def transformer_layer(x, w, heads, p=0.0, seed=0, eps=1e-12, activation="gelu"):
+    """Post-LN encoder layer composed from the oracle's own pieces (FP32/FP64):
+    q,k,v projections, attention(), output projection, add_layernorm, FFN with
+    gelu() or no activation, add_layernorm.  ``w`` uses the field names of
+    TensorFuseTransformerParams; matrices are [in, out]."""
+    f = lambda t: np.asarray(t, np.float64)
+    B, S, H = x.shape
+    x2 = f(x).reshape(B * S, H)
+    proj = lambda a, wn, bn: a @ f(w[wn]) + (f(w[bn]) if w.get(bn) is not None else 0.0)
+    q, k, v = (proj(x2, n + "_weight", n + "_bias").reshape(B, S, H) for n in ("query", "key", "value"))
+    ctx = attention(q.astype(np.float32), k.astype(np.float32), v.astype(np.float32), heads, p=p, seed=seed)
+    a = proj(f(ctx).reshape(B * S, H), "output_weight", "output_bias")
+    h1 = add_layernorm(x2, a, w["ln1_weight"], w["ln1_bias"], eps)
+    u = proj(h1, "ffn_weight1", "ffn_bias1")
+    if activation == "gelu":
+        u = 0.5 * u * (1.0 + np.tanh(0.7978845608028654 * (u + 0.044715 * u ** 3)))
+    d = proj(u, "ffn_weight2", "ffn_bias2")
+    return add_layernorm(h1, d, w["ln2_weight"], w["ln2_bias"], eps).reshape(B, S, H)
+
+
+def quantize_sym_int8(x):
+    """Per-tensor symmetric INT8 quantisation, FP32 arithmetic: scale = max|x|/127
+    (1 for an all-zero tensor), q = clip(rint(x/scale), -127, 127) with
+    round-half-even.  The reference has no quantiser of its own (its binding
+    only guesses a scale from INT8 data, src/python/core_bindings.cpp:467-491);
+    this is the recipe the INT8 benchmark configuration is generated with."""
+    x = np.asarray(x).astype(np.float32)
+    amax = np.float32(np.max(np.abs(x))) if x.size else np.float32(0)
+    scale = np.float32(amax / np.float32(127.0)) if amax > 0 else np.float32(1.0)
+    q = np.clip(np.rint(x / scale), -127, 127).astype(np.int8)
+    return q, scale
+
+
 # -------------------------------------------------------------- numpy twins
 
 def np_gelu(x):

@@ -507,6 +507,85 @@ def fused_multi_head_attention(query, key, value, output=None, num_heads=1, drop
     return output
 
 
+_LAYER_KEYS = ("query_weight", "key_weight", "value_weight", "output_weight", "query_bias", "key_bias",
+               "value_bias", "output_bias", "ffn_weight1", "ffn_weight2", "ffn_bias1", "ffn_bias2",
+               "ln1_weight", "ln1_bias", "ln2_weight", "ln2_bias")
+
+
+def fused_transformer_layer(input, weights, num_heads, dropout_prob=0.0, layer_norm_eps=1e-12, output=None,
+                            activation="gelu", use_bias=True, stream=None):
+    """One post-LN encoder layer inside the library (tensorfuse_fused_transformer_layer):
+    ``input``/``output`` [batch, seq, hidden] torch CUDA tensors (FP16 or FP32),
+    ``weights`` a dict with the TensorFuseTransformerParams field names
+    (matrices [in, out], vectors [out]).  The reference's entry point is a
+    placeholder (src/tensorfuse_c_api.cpp:313-329); this one computes."""
+    import torch
+    from ._lib import TransformerParams
+    x = input.contiguous()
+    if output is None:
+        output = torch.empty_like(x)
+    dt = _torch_dt(x)
+    params = TransformerParams()
+    keep = []
+    for name in _LAYER_KEYS:
+        t = weights.get(name)
+        if t is None:
+            continue
+        t = t.contiguous()
+        ct = _c_tensor(t.data_ptr(), tuple(t.shape), _torch_dt(t))
+        keep.append((t, ct))
+        setattr(params, name, C.pointer(ct))
+    params.num_heads = int(num_heads)
+    params.dropout_prob = float(dropout_prob)
+    params.ffn_activation = {"gelu": 2, "none": 0, "relu": 1}[activation]
+    params.layer_norm_eps = float(layer_norm_eps)
+    params.use_bias = bool(use_bias)
+    params.use_flash_attention = True
+    ti = _c_tensor(x.data_ptr(), tuple(x.shape), dt)
+    to = _c_tensor(output.data_ptr(), tuple(output.shape), _torch_dt(output))
+    with torch.cuda.device(x.device):
+        st = _auto_init(_L.tensorfuse_fused_transformer_layer, C.byref(ti), C.byref(to), C.byref(params),
+                        _torch_stream(stream, x.device))
+    _check("fused_transformer_layer", st)
+    return output
+
+
+def add_layernorm(x, residual, gamma, beta, eps=1e-12, output=None, stream=None):
+    """LayerNorm(x + residual) * gamma + beta over the last dimension (torch CUDA
+    tensors, FP16 or FP32; residual may be None)."""
+    import torch
+    x = x.contiguous()
+    if output is None:
+        output = torch.empty_like(x)
+    H = x.shape[-1]
+    with torch.cuda.device(x.device):
+        st = _auto_init(_L.tensorfuse_b200_add_layernorm, x.data_ptr(),
+                        None if residual is None else residual.contiguous().data_ptr(), gamma.data_ptr(),
+                        beta.data_ptr(), output.data_ptr(), x.numel() // H, H, int(_torch_dt(x)), float(eps),
+                        _torch_stream(stream, x.device))
+    _check("add_layernorm", st)
+    return output
+
+
+def quantize_int8(x, stream=None):
+    """Per-tensor symmetric INT8 quantisation of a torch CUDA tensor (FP16 or
+    FP32) on the device: returns ``(q, scale)`` with ``q`` int8 of x's shape and
+    ``scale`` a one-element FP32 CUDA tensor (= max|x|/127), ready to be passed
+    as a device scale to the INT8 GEMM.  No host synchronisation."""
+    import torch
+    if not (_is_torch(x) and x.is_cuda):
+        raise RuntimeError("quantize_int8 failed: " + get_error_string(Status.INVALID_ARGUMENT))
+    x = x.contiguous()
+    dt = _torch_dt(x)
+    q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    scale = torch.empty(1, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _auto_init(_L.tensorfuse_b200_quantize_int8, x.data_ptr(), int(dt), x.numel(), q.data_ptr(),
+                        scale.data_ptr(), _torch_stream(stream, x.device))
+    _check("quantize_int8", st)
+    return q, scale
+
+
 def is_gpu_supported() -> bool:
     """True on a device this build targets (compute capability 10.x)."""
     try:
@@ -518,7 +597,7 @@ def is_gpu_supported() -> bool:
 
 __all__ = ["Status", "DataType", "Config", "TensorFuseStatus", "TensorFuseDataType",
            "TensorFuseConfig", "init", "shutdown", "cleanup", "get_version", "get_error_string",
-           "fused_gemm_bias_gelu", "fused_softmax_dropout", "fused_multi_head_attention",
+           "fused_gemm_bias_gelu", "fused_softmax_dropout", "fused_multi_head_attention", "fused_transformer_layer", "add_layernorm", "quantize_int8",
            "set_random_seed", "device_ids", "watchdog_status", "launch_count", "softmax_schedule",
            "plan_shards", "pinned_empty", "is_gpu_supported", "INT8_DEQUANT", "INT8_LEGACY",
            "INT8_RAW", "TENSORFUSE_MAX_DIMS"]

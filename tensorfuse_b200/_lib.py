@@ -29,6 +29,17 @@ class Tensor(C.Structure):
                 ("scale", C.c_void_p), ("zero_point", C.c_void_p)]
 
 
+class TransformerParams(C.Structure):
+    """TensorFuseTransformerParams (include/tensorfuse/types.h)."""
+    _fields_ = [(n, C.POINTER(Tensor)) for n in (
+        "query_weight", "key_weight", "value_weight", "output_weight",
+        "query_bias", "key_bias", "value_bias", "output_bias",
+        "ffn_weight1", "ffn_weight2", "ffn_bias1", "ffn_bias2",
+        "ln1_weight", "ln1_bias", "ln2_weight", "ln2_bias")] + [
+        ("num_heads", C.c_int), ("dropout_prob", C.c_float), ("ffn_activation", C.c_int),
+        ("layer_norm_eps", C.c_float), ("use_bias", C.c_bool), ("use_flash_attention", C.c_bool)]
+
+
 class Config(C.Structure):
     """TensorFuseConfig (include/tensorfuse/types.h)."""
     _fields_ = [("device_count", C.c_int), ("device_ids", C.POINTER(C.c_int)),
@@ -77,6 +88,8 @@ def _load():
     sig("fused_softmax_dropout_fp32_wrapper", i, sm)
     sig("tensorfuse_b200_gemm_int8", i, [vp, vp, vp, vp, i, i, i, f, f, i, i, i, st])
     sig("tensorfuse_b200_gemm_bias_act", i, [vp, vp, vp, vp, i, i, i, i, i, f, f, st])
+    sig("tensorfuse_b200_add_layernorm", i, [vp, vp, vp, vp, vp, ll, i, i, f, st])
+    sig("tensorfuse_b200_quantize_int8", i, [vp, i, ll, vp, vp, st])
     sig("tensorfuse_b200_attention", i, [vp, vp, vp, vp, i, i, i, i, i] + [ll] * 12 + [i, f, f, ull, vp, st])
     sig("tensorfuse_b200_softmax_dropout_rows", i, [vp, vp, vp, ll, i, i, f, ull, ull, st])
     sig("tensorfuse_b200_softmax_schedule", None, [i, i, i, C.POINTER(i), C.POINTER(i)])

@@ -21,7 +21,7 @@ LIBDIR = os.path.join(PKG, "lib")
 OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "libtensorfuse.so")
 
-SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "runtime.cpp", "c_api.cpp",
+SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "quantize.cu", "layernorm.cu", "transformer_layer.cpp", "runtime.cpp", "c_api.cpp",
            "host_ops.cpp", "noalloc.cu", "profiler.cpp"]
 HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh", "attention_tc_kernel.cuh", "philox.cuh", "tma_host.h"]
 

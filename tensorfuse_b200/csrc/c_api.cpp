@@ -336,15 +336,7 @@ TensorFuseStatus tensorfuse_fused_multi_head_attention(const TensorFuseTensor* q
                                    nullptr, stream);
 }
 
-TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseTensor* input,
-                                                    TensorFuseTensor* output,
-                                                    const TensorFuseTransformerParams* params,
-                                                    cudaStream_t stream) {
-  (void)stream;
-  if (!Runtime::get().initialized()) return TENSORFUSE_ERROR_NOT_INITIALIZED;
-  if (!input || !output || !params) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
-  return TENSORFUSE_SUCCESS;
-}
+// tensorfuse_fused_transformer_layer: transformer_layer.cpp
 
 TensorFuseStatus tensorfuse_autotune(const TensorFuseModelConfig* model_config, const char* output_path) {
   if (!Runtime::get().initialized()) return TENSORFUSE_ERROR_NOT_INITIALIZED;
@@ -457,6 +449,21 @@ TensorFuseStatus tensorfuse_b200_attention(const void* q, const void* k, const v
   a.dtype = dtype; a.scale = scale; a.p = dropout_prob; a.seed = seed; a.kv_lengths = kv_lengths;
   OwnerGuard og(out);
   return to_status(launch_attention(a, stream));
+}
+
+TensorFuseStatus tensorfuse_b200_quantize_int8(const void* x, int dtype, long long n, signed char* q,
+                                             float* scale_dev, cudaStream_t stream) {
+  if (!x || !q || !scale_dev || n < 0) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  OwnerGuard og(q);
+  return to_status(launch_quantize_int8(x, dtype, n, q, scale_dev, stream));
+}
+
+TensorFuseStatus tensorfuse_b200_add_layernorm(const void* x, const void* residual, const void* gamma,
+                                             const void* beta, void* out, long long rows, int hidden, int dtype,
+                                             float eps, cudaStream_t stream) {
+  if (!x || !gamma || !beta || !out || rows < 0 || hidden <= 0) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  OwnerGuard og(out);
+  return to_status(launch_add_layernorm(x, residual, gamma, beta, out, rows, hidden, dtype, eps, stream));
 }
 
 void tensorfuse_b200_softmax_schedule(int row_len, int dtype, int aligned16, int* vec, int* warps) {

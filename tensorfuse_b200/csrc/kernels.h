@@ -93,6 +93,19 @@ struct AttnArgs {
 bool attention_tc_eligible(const AttnArgs& a);
 LaunchResult launch_attention(const AttnArgs& a, cudaStream_t stream);
 
+// ------------------------------------------------------ INT8 quantisation
+// Per-tensor symmetric: *scale_dev = max|x|/127 (1 for an all-zero tensor),
+// q = clip(rint(x / scale), -127, 127).  Allocates nothing: the scale word is
+// the reduction's scratch.
+LaunchResult launch_quantize_int8(const void* x, int dtype, long long n, signed char* q, float* scale_dev,
+                                  cudaStream_t stream);
+
+// ------------------------------------------------- residual + layer norm
+// out = LayerNorm(x + residual) * gamma + beta over rows of `hidden` elements
+// (residual may be null); FP32 arithmetic, x/residual/gamma/beta/out of `dtype`.
+LaunchResult launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
+                                  long long rows, int hidden, int dtype, float eps, cudaStream_t stream);
+
 // Device-side watchdog: 0 when no bounded wait has expired since the last
 // reset, else the code of the first wait that gave up.
 int watchdog_status();
