@@ -541,10 +541,15 @@ def run_encoder(args):
         "config": {"workload": "bert_large_encoder_forward", "layers": 24, "hidden": 1024, "heads": 16, "ffn": 4096,
                    "global_batch": batch, "seq_len": seq, "parallelism": f"dp{world}_batch_sharded_replicated_weights",
                    "attention": args.attention,
-                   "fused_ops": ("multi-head attention with dropout p=0.1 (one kernel)" if args.attention == "fused" else
-                                 "softmax+dropout p=0.1 on materialised scores") + ", FFN-up GEMM+bias+GELU, FFN-down GEMM+bias",
-                   "other_ops": "torch (cuBLAS projections" + ("" if args.attention == "fused" else ", attention matmuls") +
-                                ", layer norm)"},
+                   "fused_ops": {"layer": "tensorfuse_fused_transformer_layer per layer: QKV/output projections (GEMM+bias), "
+                                          "attention with dropout p=0.1 (one kernel), residual+LayerNorm, FFN-up GEMM+bias+GELU, "
+                                          "FFN-down GEMM+bias",
+                                 "fused": "multi-head attention with dropout p=0.1 (one kernel), FFN-up GEMM+bias+GELU, "
+                                          "FFN-down GEMM+bias",
+                                 "unfused": "softmax+dropout p=0.1 on materialised scores, FFN-up GEMM+bias+GELU, "
+                                            "FFN-down GEMM+bias"}[args.attention],
+                   "other_ops": {"layer": "none", "fused": "torch (cuBLAS projections, layer norm)",
+                                 "unfused": "torch (cuBLAS projections, attention matmuls, layer norm)"}[args.attention]},
         "effective_tflops": flop / (ms * 1e-3) / 1e12,
         "gpu_launches": int(tf.launch_count() - launches0)}), flush=True)
     return 0
@@ -556,8 +561,9 @@ def main():
                     help="gemm_fp16 = the headline (default); bert_large = encoder forward, tokens/s")
     ap.add_argument("--only", default=None, choices=["gemm_fp16", "gemm_int8", "softmax", "softmax_p0", "attention", "attention_p0"],
                     help="run a single kernel a few times (profiling aid)")
-    ap.add_argument("--attention", default="fused", choices=["fused", "unfused"],
-                    help="bert_large workload: one fused attention kernel, or softmax+dropout between two matmuls")
+    ap.add_argument("--attention", default="layer", choices=["layer", "fused", "unfused"],
+                    help="bert_large workload: whole layers inside the library (tensorfuse_fused_transformer_layer), "
+                         "the fused attention kernel between torch projections, or softmax+dropout between two matmuls")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)

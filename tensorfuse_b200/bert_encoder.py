@@ -7,7 +7,9 @@ norms; libtensorfuse.so does
   * attention: fused_multi_head_attention straight on the fused QKV buffer (the
     probabilities never reach memory), or, with attention="unfused", the
     attention probabilities through fused_softmax_dropout on [b, heads, S, S]
-    scores between two torch matmuls,
+    scores between two torch matmuls; with attention="layer" each layer is one
+    call of tensorfuse_fused_transformer_layer (projections, attention, both
+    layer norms and the FFN inside the library, no torch operator on the path),
   * FFN-up:   fused GEMM + bias + GELU,
   * FFN-down: fused GEMM + bias (activation NONE).
 The batch dimension is the sharding dimension: each GPU (one process per GPU)
@@ -61,6 +63,21 @@ def gemm_bias_act(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, activation:
     return out
 
 
+def layer_params(p: dict, cfg: EncoderConfig) -> dict:
+    """The weights of one layer under the field names of TensorFuseTransformerParams
+    (separate, contiguous Q/K/V projections), cached in the layer's dict."""
+    if "_params" not in p:
+        H = cfg.hidden
+        p["_params"] = {
+            "query_weight": p["wqkv"][:, :H].contiguous(), "key_weight": p["wqkv"][:, H:2 * H].contiguous(),
+            "value_weight": p["wqkv"][:, 2 * H:].contiguous(), "output_weight": p["wo"],
+            "query_bias": p["bqkv"][:H].contiguous(), "key_bias": p["bqkv"][H:2 * H].contiguous(),
+            "value_bias": p["bqkv"][2 * H:].contiguous(), "output_bias": p["bo"],
+            "ffn_weight1": p["w1"], "ffn_weight2": p["w2"], "ffn_bias1": p["b1"], "ffn_bias2": p["b2"],
+            "ln1_weight": p["ln1_g"], "ln1_bias": p["ln1_b"], "ln2_weight": p["ln2_g"], "ln2_bias": p["ln2_b"]}
+    return p["_params"]
+
+
 def layer_seed(seed: int, layer: int) -> int:
     return (seed * 1000003 + layer * 131) & 0xFFFFFFFFFFFF
 
@@ -76,6 +93,13 @@ def encoder_forward(x: torch.Tensor, layers, cfg: EncoderConfig, seed: int = 4, 
     Bsz, S, H = x.shape
     nh, d = cfg.heads, H // cfg.heads
     scale = 1.0 / math.sqrt(d)
+    if attention == "layer":
+        # every layer is one call of tensorfuse_fused_transformer_layer: no torch operator on the path
+        tf.set_random_seed(seed)
+        h3 = x.contiguous()
+        for p in layers:
+            h3 = tf.fused_transformer_layer(h3, layer_params(p, cfg), nh, cfg.dropout, cfg.eps)
+        return h3
     h = x.reshape(Bsz * S, H).contiguous()
     for li, p in enumerate(layers):
         qkv = torch.addmm(p["bqkv"], h, p["wqkv"])

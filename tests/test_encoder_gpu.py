@@ -35,8 +35,9 @@ def test_small_encoder_matches_fp32_reference(tf, dropout):
     assert err < 3e-2, err
 
 
+@pytest.mark.parametrize("mode", ["fused", "layer"])
 @pytest.mark.parametrize("dropout", [0.0, 0.1])
-def test_small_encoder_with_fused_attention(tf, dropout):
+def test_small_encoder_with_fused_attention(tf, dropout, mode):
     from tensorfuse_b200 import bert_encoder as be
     cfg = be.EncoderConfig(layers=3, hidden=256, heads=4, ffn=1024, dropout=dropout)
     dev = torch.device("cuda")
@@ -48,13 +49,17 @@ def test_small_encoder_with_fused_attention(tf, dropout):
     B, S = 5, 128
     x = torch.randn((B, S, cfg.hidden), generator=g).to(dev, torch.float16)
     with torch.no_grad():
-        y = be.encoder_forward(x, layers, cfg, seed=7)
+        y = be.encoder_forward(x, layers, cfg, seed=7, attention=mode)
         # the decisions the fused operator makes are those of the softmax+dropout operator with the same seed
         masks = None
         if dropout > 0:
             zeros = torch.zeros((B, cfg.heads, S, S), dtype=torch.float16, device=dev)
-            masks = [tf.fused_softmax_dropout(zeros, dropout_prob=dropout, seed=be.layer_seed(7, li))[1]
-                     for li in range(cfg.layers)]
+            if mode == "layer":      # seeds come from the library's seed source, restarted at the same point
+                tf.set_random_seed(7)
+                masks = [tf.fused_softmax_dropout(zeros, dropout_prob=dropout)[1] for _ in range(cfg.layers)]
+            else:
+                masks = [tf.fused_softmax_dropout(zeros, dropout_prob=dropout, seed=be.layer_seed(7, li))[1]
+                         for li in range(cfg.layers)]
         ref = be.reference_forward(x, layers, cfg, masks=masks)
     torch.cuda.synchronize()
     assert tf.watchdog_status() == 0
