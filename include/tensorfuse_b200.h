@@ -77,8 +77,19 @@ TensorFuseStatus tensorfuse_b200_gemm_int8(const void* A, const void* B, const v
                                            int bias_dtype, int out_dtype, int epilogue,
                                            cudaStream_t stream);
 
-/* C = act(alpha * A[M,K] * B[K,N] + beta * bias[N]) for FP16 or FP32 operands
- * (dtype), activation = TENSORFUSE_ACTIVATION_GELU or TENSORFUSE_ACTIVATION_NONE.
+/* FP8 (E4M3, one byte per element, as in TENSORFUSE_FP8_E4M3) operands with
+ * per-tensor dequantisation factors: C = gelu(acc * scale_A * scale_B + bias),
+ * FP32 accumulation on the tensor cores, FP16 or FP32 bias and output.  The
+ * reference enumerates the type (src/tensorfuse/types.h:56) and has no kernel
+ * for it.  Through the struct entry point the scales are the device-resident
+ * `scale` fields of the input and weight tensors, exactly as for INT8. */
+TensorFuseStatus tensorfuse_b200_gemm_fp8(const void* A, const void* B, const void* bias, void* C,
+                                          int M, int N, int K, float scale_A, float scale_B,
+                                          int bias_dtype, int out_dtype, cudaStream_t stream);
+
+/* C = act(alpha * A[M,K] * B[K,N] + beta * bias[N]) for FP16, BF16 or FP32 operands
+ * (dtype; BF16 is also accepted by tensorfuse_fused_gemm_bias_gelu, which the
+ * reference enumerates in src/tensorfuse/types.h:52 without a kernel), activation = TENSORFUSE_ACTIVATION_GELU or TENSORFUSE_ACTIVATION_NONE.
  * NONE is the FFN-down form: the reference's benchmark applies GELU to that
  * projection too because its only entry point always does
  * (benchmarks/bert_baseline.cu:318-322); the activation enum is the reference's

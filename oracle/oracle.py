@@ -222,6 +222,50 @@ def transformer_layer(x, w, heads, p=0.0, seed=0, eps=1e-12, activation="gelu"):
     return add_layernorm(h1, d, w["ln2_weight"], w["ln2_bias"], eps).reshape(B, S, H)
 
 
+def bf16_round(x):
+    """FP32 -> BF16 (round to nearest even) -> FP32, on the bit patterns."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return r.astype(np.uint32).view(np.float32).reshape(np.shape(x))
+
+
+def bf16_bits(x):
+    """FP32 values (already BF16-representable) -> their 16-bit patterns."""
+    return (np.ascontiguousarray(x, np.float32).view(np.uint32) >> 16).astype(np.uint16).reshape(np.shape(x))
+
+
+def bf16_from_bits(b):
+    return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32).reshape(np.shape(b))
+
+
+def fp8_e4m3_table():
+    """Value of each of the 256 E4M3 byte patterns (OCP FP8 "fn" variant: bias 7,
+    no infinities, 0x7F / 0xFF are NaN), the type TENSORFUSE_FP8_E4M3 names
+    (reference src/tensorfuse/types.h:56)."""
+    t = np.empty(256, np.float32)
+    for b in range(256):
+        sgn = -1.0 if b & 0x80 else 1.0
+        e, m = (b >> 3) & 0xF, b & 7
+        if e == 15 and m == 7:
+            v = np.nan
+        elif e == 0:
+            v = m / 8.0 * 2.0 ** -6
+        else:
+            v = (1 + m / 8.0) * 2.0 ** (e - 7)
+        t[b] = sgn * v
+    return t
+
+
+def gemm_bias_gelu_f64(A, B, bias, scale=1.0, activation="gelu"):
+    """gelu(scale * A @ B + bias) in float64 from already-widened operands: the
+    semantics of gemm_bias_gelu_ref (reference src/tests/test_kernels.cu:43-64)
+    carried out in double, for operand types the C loops do not cover."""
+    x = scale * (np.asarray(A, np.float64) @ np.asarray(B, np.float64)) + np.asarray(bias, np.float64)
+    if activation == "gelu":
+        x = 0.5 * x * (1.0 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))
+    return x
+
+
 def quantize_sym_int8(x):
     """Per-tensor symmetric INT8 quantisation, FP32 arithmetic: scale = max|x|/127
     (1 for an all-zero tensor), q = clip(rint(x/scale), -127, 127) with

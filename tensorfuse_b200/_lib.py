@@ -87,6 +87,7 @@ def _load():
     sig("fused_softmax_dropout_fp16_wrapper", i, sm)
     sig("fused_softmax_dropout_fp32_wrapper", i, sm)
     sig("tensorfuse_b200_gemm_int8", i, [vp, vp, vp, vp, i, i, i, f, f, i, i, i, st])
+    sig("tensorfuse_b200_gemm_fp8", i, [vp, vp, vp, vp, i, i, i, f, f, i, i, st])
     sig("tensorfuse_b200_gemm_bias_act", i, [vp, vp, vp, vp, i, i, i, i, i, f, f, st])
     sig("tensorfuse_b200_add_layernorm", i, [vp, vp, vp, vp, vp, ll, i, i, f, st])
     sig("tensorfuse_b200_quantize_int8", i, [vp, i, ll, vp, vp, st])

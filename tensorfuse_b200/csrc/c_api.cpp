@@ -256,8 +256,24 @@ TensorFuseStatus tensorfuse_fused_gemm_bias_gelu(const TensorFuseTensor* input,
       return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
     return TENSORFUSE_ERROR_INVALID_ARGUMENT;
   }
+  if (input->dtype == TENSORFUSE_FP8_E4M3) {
+    // FP8 operands with per-tensor dequantisation scales (device pointers, as for INT8):
+    // out = gelu(acc * sA * sB + bias), FP16 or FP32 output
+    if (weight->dtype != TENSORFUSE_FP8_E4M3) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+    if ((output->dtype != TENSORFUSE_FLOAT16 && output->dtype != TENSORFUSE_FLOAT32) ||
+        (bias->dtype != TENSORFUSE_FLOAT16 && bias->dtype != TENSORFUSE_FLOAT32))
+      return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+    return gemm_flat(input->data, weight->data, bias->data, output->data, M, N, K, kFp8E4M3,
+                     bias->dtype == TENSORFUSE_FLOAT16 ? kF16 : kF32, output->dtype == TENSORFUSE_FLOAT16 ? kF16 : kF32,
+                     kEpiI8Dequant, 1.0f, 1.0f, 1.0f, static_cast<const float*>(input->scale),
+                     static_cast<const float*>(weight->scale), stream);
+  }
   if (input->dtype != weight->dtype || input->dtype != output->dtype)
     return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  if (input->dtype == TENSORFUSE_BFLOAT16)
+    return gemm_flat(input->data, weight->data, bias->data, output->data, M, N, K, kBF16,
+                     bias->dtype == TENSORFUSE_FLOAT32 ? kF32 : kBF16, kBF16, kEpiGelu, alpha, beta, 1.0f, nullptr,
+                     nullptr, stream);
   if (input->dtype == TENSORFUSE_FLOAT16)
     return tk::fused_gemm_bias_gelu_fp16(input->data, weight->data, bias->data, output->data, M, N, K,
                                          alpha, beta, stream);
@@ -404,6 +420,15 @@ TensorFuseStatus tensorfuse_b200_gemm_int8(const void* A, const void* B, const v
                    scale_A * scale_B, nullptr, nullptr, stream);
 }
 
+TensorFuseStatus tensorfuse_b200_gemm_fp8(const void* A, const void* B, const void* bias, void* C, int M,
+                                        int N, int K, float scale_A, float scale_B, int bias_dtype,
+                                        int out_dtype, cudaStream_t stream) {
+  if (out_dtype != kF16 && out_dtype != kF32) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  if (bias_dtype != kF16 && bias_dtype != kF32) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  return gemm_flat(A, B, bias, C, M, N, K, kFp8E4M3, bias_dtype, out_dtype, kEpiI8Dequant, 1.0f, 1.0f,
+                   scale_A * scale_B, nullptr, nullptr, stream);
+}
+
 TensorFuseStatus tensorfuse_b200_softmax_dropout_rows(const void* input, void* output,
                                                       unsigned char* dropout_mask, long long rows,
                                                       int row_len, int dtype, float dropout_prob,
@@ -420,7 +445,7 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_rows(const void* input, void* o
 TensorFuseStatus tensorfuse_b200_gemm_bias_act(const void* A, const void* B, const void* bias, void* C, int M,
                                              int N, int K, int dtype, int activation, float alpha, float beta,
                                              cudaStream_t stream) {
-  if (dtype != kF16 && dtype != kF32) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  if (dtype != kF16 && dtype != kF32 && dtype != kBF16) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
   int epi;
   if (activation == TENSORFUSE_ACTIVATION_GELU) epi = kEpiGelu;
   else if (activation == TENSORFUSE_ACTIVATION_NONE) epi = kEpiLinear;

@@ -8,7 +8,9 @@
 // 128x128 output tile per CTA, K step 8, 256 threads, 8x8 accumulators per
 // thread held in registers; bias, activation and the conversion to the output
 // type are applied to those registers and stored once.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include "epilogue.cuh"
 #include "kernels.h"
@@ -21,16 +23,21 @@ constexpr int BM = 128, BN = 128, BK = 8;
 template <typename T> struct AccOf { using type = float; };
 template <> struct AccOf<int8_t> { using type = int; };
 
-template <typename TIn, typename TAcc>
-__device__ __forceinline__ TAcc widen(TIn v) {
-  if constexpr (sizeof(TIn) == 2) return __half2float(v);
-  else return (TAcc)v;
-}
+template <typename TAcc> __device__ __forceinline__ TAcc widen(float v) { return (TAcc)v; }
+template <typename TAcc> __device__ __forceinline__ TAcc widen(int8_t v) { return (TAcc)v; }
+template <typename TAcc> __device__ __forceinline__ TAcc widen(__half v) { return (TAcc)__half2float(v); }
+template <typename TAcc> __device__ __forceinline__ TAcc widen(__nv_bfloat16 v) { return (TAcc)__bfloat162float(v); }
+template <typename TAcc> __device__ __forceinline__ TAcc widen(__nv_fp8_e4m3 v) { return (TAcc)float(v); }
 
 __device__ __forceinline__ float load_bias(const void* bias, int bias_dtype, int n) {
   if (bias_dtype == kF16) return __half2float(static_cast<const __half*>(bias)[n]);
+  if (bias_dtype == kBF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n]);
   return static_cast<const float*>(bias)[n];
 }
+__device__ __forceinline__ void store_out(float* p, float v) { *p = v; }
+__device__ __forceinline__ void store_out(__half* p, float v) { *p = __float2half_rn(v); }
+__device__ __forceinline__ void store_out(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void store_out(int* p, float v) { *p = __float_as_int(v); }
 
 template <typename TIn, typename TOut, int EPI>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ A,
@@ -60,9 +67,9 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ 
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int gm = m0 + a_row, gk = k0 + a_k + i;
-      As[a_k + i][a_row] = (gm < M && gk < K) ? widen<TIn, TAcc>(A[(size_t)gm * K + gk]) : (TAcc)0;
+      As[a_k + i][a_row] = (gm < M && gk < K) ? widen<TAcc>(A[(size_t)gm * K + gk]) : (TAcc)0;
       const int gkb = k0 + b_k, gn = n0 + b_n + i;
-      Bs[b_k][b_n + i] = (gkb < K && gn < N) ? widen<TIn, TAcc>(B[(size_t)gkb * N + gn]) : (TAcc)0;
+      Bs[b_k][b_n + i] = (gkb < K && gn < N) ? widen<TAcc>(B[(size_t)gkb * N + gn]) : (TAcc)0;
     }
     __syncthreads();
 #pragma unroll
@@ -95,8 +102,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ 
       if (gm >= M) continue;
       const float v = epilogue_value<EPI, kFp32Out>(acc[i][j], bv, ep);
       if constexpr (EPI == kEpiI8Raw) C[(size_t)gm * N + gn] = (TOut)acc[i][j];
-      else if constexpr (sizeof(TOut) == 2) C[(size_t)gm * N + gn] = __float2half_rn(v);
-      else C[(size_t)gm * N + gn] = v;
+      else store_out(C + (size_t)gm * N + gn, v);
     }
   }
 }
@@ -118,7 +124,7 @@ LaunchResult run(const GemmArgs& a, cudaStream_t stream) {
 LaunchResult launch_gemm_simt(const GemmArgs& a, cudaStream_t stream) {
   if (!a.A || !a.B || !a.C || (!a.bias && a.epilogue != kEpiI8Raw)) return kInvalidArgument;
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return kInvalidArgument;
-  if (a.bias_dtype != kF32 && a.bias_dtype != kF16) return kUnsupported;
+  if (a.bias_dtype != kF32 && a.bias_dtype != kF16 && a.bias_dtype != kBF16) return kUnsupported;
   if (a.in_dtype == kF32 && a.out_dtype == kF32 && a.epilogue == kEpiGelu)
     return run<float, float, kEpiGelu>(a, stream);
   if (a.in_dtype == kF16 && a.out_dtype == kF16 && a.epilogue == kEpiGelu)
@@ -127,6 +133,14 @@ LaunchResult launch_gemm_simt(const GemmArgs& a, cudaStream_t stream) {
     return run<float, float, kEpiLinear>(a, stream);
   if (a.in_dtype == kF16 && a.out_dtype == kF16 && a.epilogue == kEpiLinear)
     return run<__half, __half, kEpiLinear>(a, stream);
+  if (a.in_dtype == kBF16 && a.out_dtype == kBF16 && a.epilogue == kEpiGelu)
+    return run<__nv_bfloat16, __nv_bfloat16, kEpiGelu>(a, stream);
+  if (a.in_dtype == kBF16 && a.out_dtype == kBF16 && a.epilogue == kEpiLinear)
+    return run<__nv_bfloat16, __nv_bfloat16, kEpiLinear>(a, stream);
+  if (a.in_dtype == kFp8E4M3 && a.epilogue == kEpiI8Dequant) {
+    if (a.out_dtype == kF16) return run<__nv_fp8_e4m3, __half, kEpiI8Dequant>(a, stream);
+    if (a.out_dtype == kF32) return run<__nv_fp8_e4m3, float, kEpiI8Dequant>(a, stream);
+  }
   if (a.in_dtype == kI8) {
     if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF16) return run<int8_t, __half, kEpiI8Dequant>(a, stream);
     if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF32) return run<int8_t, float, kEpiI8Dequant>(a, stream);

@@ -7,6 +7,7 @@
 // three-kernel INT8 path (per-call transpose of B, GEMM, apply_scaled_gelu_kernel:
 // reference src/kernels/fused_gemm_bias_gelu_int8.cu:156-344) with one launch.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <mutex>
@@ -114,14 +115,16 @@ LaunchResult run(const GemmArgs& a, cudaStream_t stream) {
 }  // namespace
 
 bool gemm_tc_eligible(const GemmArgs& a) {
-  if (a.in_dtype != kF16 && a.in_dtype != kI8) return false;
+  if (a.in_dtype != kF16 && a.in_dtype != kBF16 && a.in_dtype != kI8 && a.in_dtype != kFp8E4M3) return false;
   if (a.M <= 0 || a.N <= 0 || a.K <= 0) return false;
-  const int es = a.in_dtype == kF16 ? 2 : 1;
-  const int out_es = a.out_dtype == kF16 ? 2 : 4;
+  const int es = (a.in_dtype == kF16 || a.in_dtype == kBF16) ? 2 : 1;
+  const int out_es = (a.out_dtype == kF16 || a.out_dtype == kBF16) ? 2 : 4;
   const uintptr_t ptrs = (uintptr_t)a.A | (uintptr_t)a.B | (uintptr_t)a.C;
   if (ptrs & 15u) return false;
   if (((size_t)a.K * es) % 16 || ((size_t)a.N * es) % 16 || ((size_t)a.N * out_es) % 16) return false;
   if (a.in_dtype == kF16) return a.out_dtype == kF16 && (a.epilogue == kEpiGelu || a.epilogue == kEpiLinear);
+  if (a.in_dtype == kBF16) return a.out_dtype == kBF16 && (a.epilogue == kEpiGelu || a.epilogue == kEpiLinear);
+  if (a.in_dtype == kFp8E4M3) return a.epilogue == kEpiI8Dequant && (a.out_dtype == kF16 || a.out_dtype == kF32);
   return (a.epilogue == kEpiI8Dequant && (a.out_dtype == kF16 || a.out_dtype == kF32)) ||
          (a.epilogue == kEpiI8Legacy && a.out_dtype == kF32) ||
          (a.epilogue == kEpiI8Raw && a.out_dtype == kI32);
@@ -132,6 +135,10 @@ LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   if (!a.bias && a.epilogue != kEpiI8Raw) return kInvalidArgument;
   if (a.in_dtype == kF16 && a.epilogue == kEpiLinear) return run<0, kEpiLinear, __half>(a, stream);
   if (a.in_dtype == kF16) return run<0, kEpiGelu, __half>(a, stream);
+  if (a.in_dtype == kBF16 && a.epilogue == kEpiLinear) return run<2, kEpiLinear, __nv_bfloat16>(a, stream);
+  if (a.in_dtype == kBF16) return run<2, kEpiGelu, __nv_bfloat16>(a, stream);
+  if (a.in_dtype == kFp8E4M3 && a.out_dtype == kF16) return run<3, kEpiI8Dequant, __half>(a, stream);
+  if (a.in_dtype == kFp8E4M3) return run<3, kEpiI8Dequant, float>(a, stream);
   if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF16) return run<1, kEpiI8Dequant, __half>(a, stream);
   if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF32) return run<1, kEpiI8Dequant, float>(a, stream);
   if (a.epilogue == kEpiI8Legacy) return run<1, kEpiI8Legacy, float>(a, stream);

@@ -37,6 +37,7 @@
 // the tear-down that frees TMEM.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "epilogue.cuh"
@@ -84,6 +85,18 @@ template <> struct KindTraits<1> {  // INT8 operands, INT32 accumulate
   static constexpr uint32_t C_FORMAT = 2u, AB_FORMAT = 1u;
   static constexpr bool kIntAcc = true;
 };
+template <> struct KindTraits<2> {  // BF16 operands, FP32 accumulate (kind::f16, format 1)
+  static constexpr int ES = 2;
+  static constexpr uint32_t C_FORMAT = 1u, AB_FORMAT = 1u;
+  static constexpr bool kIntAcc = false;
+};
+template <> struct KindTraits<3> {  // FP8 E4M3 operands, FP32 accumulate (kind::f8f6f4, format 0)
+  static constexpr int ES = 1;
+  static constexpr uint32_t C_FORMAT = 1u, AB_FORMAT = 0u;
+  static constexpr bool kIntAcc = false;
+};
+template <typename T> struct IsBf16 { static constexpr bool value = false; };
+template <> struct IsBf16<__nv_bfloat16> { static constexpr bool value = true; };
 
 // Tile index -> (row tile, column tile): panels of PANEL_TILES_N tile columns,
 // inside a panel the column index runs fastest.
@@ -170,7 +183,11 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const fl
     const float4 b4 = *reinterpret_cast<const float4*>(bs + i);
     const float2 v0 = epilogue_pair<EPI, kFp32Out, INT_ACC>(r[i], r[i + 1], b4.x, b4.y, ep);
     const float2 v1 = epilogue_pair<EPI, kFp32Out, INT_ACC>(r[i + 2], r[i + 3], b4.z, b4.w, ep);
-    if constexpr (sizeof(TOut) == 2) {
+    if constexpr (IsBf16<TOut>::value) {
+      const __nv_bfloat162 h0 = __floats2bfloat162_rn(v0.x, v0.y), h1 = __floats2bfloat162_rn(v1.x, v1.y);
+      w[i / 2] = *reinterpret_cast<const uint32_t*>(&h0);
+      w[i / 2 + 1] = *reinterpret_cast<const uint32_t*>(&h1);
+    } else if constexpr (sizeof(TOut) == 2) {
       const __half2 h0 = __floats2half2_rn(v0.x, v0.y), h1 = __floats2half2_rn(v1.x, v1.y);
       w[i / 2] = *reinterpret_cast<const uint32_t*>(&h0);
       w[i / 2 + 1] = *reinterpret_cast<const uint32_t*>(&h1);
@@ -281,8 +298,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t adesc = make_smem_desc(a0 + j * 32, 16, 1024);
             const uint64_t bdesc = make_smem_desc(b0 + j * B_K_STEP_BYTES, B_BOX_BYTES, 1024);
             const uint32_t accumulate = (kb | j) != 0 ? 1u : 0u;
-            if (KIND == 0) tc_mma_f16(d, adesc, bdesc, IDESC, accumulate);
-            else tc_mma_i8(d, adesc, bdesc, IDESC, accumulate);
+            if (KIND == 0 || KIND == 2) tc_mma_f16(d, adesc, bdesc, IDESC, accumulate);
+            else if (KIND == 1) tc_mma_i8(d, adesc, bdesc, IDESC, accumulate);
+            else tc_mma_f8(d, adesc, bdesc, IDESC, accumulate);
           }
           tc_commit(empty_bar(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -310,8 +328,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       if (EPI != kEpiI8Raw) {
         const int n = n0 + e;
         float bv = 0.0f;
-        if (n < N) bv = bias_dtype == kF16 ? __half2float(static_cast<const __half*>(bias)[n])
-                                           : static_cast<const float*>(bias)[n];
+        if (n < N) bv = bias_dtype == kF16    ? __half2float(static_cast<const __half*>(bias)[n])
+                        : bias_dtype == kBF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n])
+                                              : static_cast<const float*>(bias)[n];
         bs[e] = bv;
       }
       mbar_arrive(bias_bar(buf));

@@ -7,7 +7,7 @@
 namespace tfb {
 
 // Storage types as seen by the launchers (values equal TensorFuseDataType).
-enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kI8 = 3, kU8 = 4, kI32 = 5 };
+enum DType : int { kF32 = 0, kF16 = 1, kBF16 = 2, kI8 = 3, kU8 = 4, kI32 = 5, kFp8E4M3 = 6, kFp8E5M2 = 7 };
 
 // Result of a launcher; mapped 1:1 on TensorFuseStatus by the ABI layer.
 enum LaunchResult : int {
@@ -39,7 +39,7 @@ LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* ma
 // ------------------------------------------------------ GEMM + bias + GELU
 enum Epilogue : int {
   kEpiGelu = 0,        // out = gelu(alpha*acc + beta*bias)                 (FP32 / FP16 paths)
-  kEpiI8Dequant = 1,   // out = gelu(fma(float(acc), scale, bias))          (INT8, multiply convention)
+  kEpiI8Dequant = 1,   // out = gelu(fma(float(acc), scale, bias))          (INT8 and FP8 operands, multiply convention)
   kEpiI8Legacy = 2,    // out = gelu_clamped(acc/scale + bias)*scale, non-finite -> 0 (INT8, reference convention)
   kEpiI8Raw = 3,       // out = acc (INT32), no bias, no activation
   kEpiLinear = 4,      // out = alpha*acc + beta*bias, no activation        (FP32 / FP16 paths, e.g. FFN-down)
@@ -51,9 +51,9 @@ struct GemmArgs {
   const void* bias;  // [N]
   void* C;           // [M,N] row-major
   int M, N, K;
-  int in_dtype;      // kF32 | kF16 | kI8
-  int bias_dtype;    // kF32 | kF16
-  int out_dtype;     // kF32 | kF16 | kI32
+  int in_dtype;      // kF32 | kF16 | kBF16 | kI8 | kFp8E4M3
+  int bias_dtype;    // kF32 | kF16 | kBF16
+  int out_dtype;     // kF32 | kF16 | kBF16 | kI32
   int epilogue;
   float alpha, beta, scale;       // scale: product of the host-known dequant factors
   const float* scale_a_dev;       // optional device pointers to one float each; multiplied
@@ -61,7 +61,7 @@ struct GemmArgs {
 };
 
 // True when the tensor-core (TMA + tcgen05) kernel can take this problem:
-// FP16 or INT8 operands, 16-byte aligned base pointers and row pitches.
+// FP16, BF16, INT8 or FP8-E4M3 operands, 16-byte aligned base pointers and row pitches.
 bool gemm_tc_eligible(const GemmArgs& a);
 LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
 // Any shape, any alignment; CUDA-core FMA kernel with the same fused epilogue.

@@ -161,6 +161,15 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d, uint64_t adesc, uint64_t b
       ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// kind::f8f6f4 with 8-bit operands (E4M3 / E5M2 stored one byte per element), FP32 accumulate.
+__device__ __forceinline__ void tc_mma_f8(uint32_t d, uint64_t adesc, uint64_t bdesc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // 32 lanes x 32 consecutive 32-bit columns: thread i of the warp receives the
 // 32 columns of TMEM lane (lane_base + i).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -212,7 +221,8 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 
 // Instruction descriptor for kind::f16 / kind::i8, dense, no negate, no
 // saturate.  a K-major, b MN-major (B is stored [K,N] with N contiguous).
-//   c_format: 1 = F32, 2 = S32;  ab_format: f16 kind 0 = F16, i8 kind 1 = S8
+//   c_format: 1 = F32, 2 = S32;  ab_format: f16 kind 0 = F16, 1 = BF16; i8 kind 1 = S8;
+//   f8f6f4 kind 0 = E4M3, 1 = E5M2
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t c_format, uint32_t ab_format,
                                                   uint32_t m, uint32_t n) {
   return (c_format << 4) | (ab_format << 7) | (ab_format << 10) | (0u << 15) | (1u << 16) |
