@@ -451,6 +451,32 @@ def run_only(args):
         fn = lambda: L.tensorfuse_b200_gemm_int8(A.data_ptr(), B.data_ptr(), b.data_ptr(), C.data_ptr(), Mi, Ni, Ki,
                                                  1e-2, 1e-4, 1, 1, 1, sp)
         work, unit = 2.0 * Mi * Ni * Ki / 1e12, "TOPS"
+    elif args.only == "gemm_bf16":
+        A = torch.randn((M, K), device=dev).bfloat16(); B = (torch.randn((K, N), device=dev) / 32).bfloat16()
+        b = (torch.randn(N, device=dev) * 0.02).bfloat16(); C = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        fn = lambda: L.tensorfuse_b200_gemm_bias_act(A.data_ptr(), B.data_ptr(), b.data_ptr(), C.data_ptr(), M, N, K,
+                                                     2, 2, 1.0, 1.0, sp)
+        work, unit = FLOP_PER_STEP / 1e12, "TFLOPS"
+    elif args.only == "gemm_fp8":
+        Mi, Ki, Ni = 8192, 4096, 16384             # the INT8 configuration's shape with E4M3 operands
+        A = torch.randn((Mi, Ki), device=dev).to(torch.float8_e4m3fn)
+        B = (torch.randn((Ki, Ni), device=dev)).to(torch.float8_e4m3fn)
+        b = (torch.randn(Ni, device=dev) * 0.02).half(); C = torch.empty((Mi, Ni), dtype=torch.float16, device=dev)
+        fn = lambda: L.tensorfuse_b200_gemm_fp8(A.data_ptr(), B.data_ptr(), b.data_ptr(), C.data_ptr(), Mi, Ni, Ki,
+                                                1.0, 1.0 / 64, 1, 1, sp)
+        work, unit = 2.0 * Mi * Ni * Ki / 1e12, "TFLOPS"
+    elif args.only in ("layernorm", "quantize"):
+        rows, Hh = 131072, 1024                      # the token matrix of the BERT-large workload
+        x = torch.randn((rows, Hh), device=dev).half(); r = torch.randn((rows, Hh), device=dev).half()
+        g = torch.ones(Hh, device=dev).half(); bt = torch.zeros(Hh, device=dev).half(); o = torch.empty_like(x)
+        q = torch.empty((rows, Hh), dtype=torch.int8, device=dev); sc = torch.empty(1, device=dev)
+        if args.only == "layernorm":
+            fn = lambda: L.tensorfuse_b200_add_layernorm(x.data_ptr(), r.data_ptr(), g.data_ptr(), bt.data_ptr(),
+                                                         o.data_ptr(), rows, Hh, 1, 1e-12, sp)
+            work, unit = rows * Hh * 6 / 1e9, "GB/s"        # two FP16 reads + one FP16 write
+        else:
+            fn = lambda: L.tensorfuse_b200_quantize_int8(x.data_ptr(), 1, rows * Hh, q.data_ptr(), sc.data_ptr(), sp)
+            work, unit = rows * Hh * 5 / 1e9, "GB/s"        # two FP16 reads + one INT8 write
     elif args.only in ("attention", "attention_p0"):
         Bq, Sq, Hh, hd = 32, 512, 16, 64           # BERT-large attention, 32 sequences
         qkv = torch.randn((Bq, Sq, 3, Hh * hd), device=dev).half()
@@ -559,7 +585,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--workload", default="gemm_fp16", choices=["gemm_fp16", "bert_large"],
                     help="gemm_fp16 = the headline (default); bert_large = encoder forward, tokens/s")
-    ap.add_argument("--only", default=None, choices=["gemm_fp16", "gemm_int8", "softmax", "softmax_p0", "attention", "attention_p0"],
+    ap.add_argument("--only", default=None, choices=["gemm_fp16", "gemm_int8", "gemm_bf16", "gemm_fp8", "softmax", "softmax_p0", "attention", "attention_p0",
+                             "layernorm", "quantize"],
                     help="run a single kernel a few times (profiling aid)")
     ap.add_argument("--attention", default="layer", choices=["layer", "fused", "unfused"],
                     help="bert_large workload: whole layers inside the library (tensorfuse_fused_transformer_layer), "

@@ -252,6 +252,7 @@ def _c_tensor(ptr: int, shape, dtype: DataType, scale_ptr: int | None = None) ->
 def _torch_dt(t):
     import torch
     return {torch.float32: DataType.FLOAT32, torch.float16: DataType.FLOAT16,
+            torch.bfloat16: DataType.BFLOAT16, torch.float8_e4m3fn: DataType.FP8_E4M3,
             torch.int8: DataType.INT8, torch.int32: DataType.INT32,
             torch.uint8: DataType.UINT8}[t.dtype]
 
@@ -362,6 +363,22 @@ def _gemm_torch_cuda(x, w, b, out, stream, scales, out_dtype, int8_mode):
                 st = _L.tensorfuse_b200_gemm_int8(x.data_ptr(), w.data_ptr(), b.data_ptr(),
                                                   out.data_ptr(), M, N, K, sA, sB, int(_torch_dt(b)),
                                                   int(_torch_dt(out)), int(int8_mode), s)
+        elif in_dt == DataType.FP8_E4M3:
+            # E4M3 operands, per-tensor dequantisation factors (floats or one-element CUDA tensors)
+            odt = out_dtype if out_dtype is not None else (out.dtype if out is not None else torch.float16)
+            if out is None:
+                out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=odt, device=x.device)
+            if scales is not None and _is_torch(scales[0]):
+                ti = _c_tensor(x.data_ptr(), (M, x.shape[-1]), in_dt, scales[0].data_ptr())
+                tw = _c_tensor(w.data_ptr(), (K, N), in_dt, scales[1].data_ptr())
+                tb = _c_tensor(b.data_ptr(), (N,), _torch_dt(b))
+                to = _c_tensor(out.data_ptr(), (M, N), _torch_dt(out))
+                st = _auto_init(_L.tensorfuse_fused_gemm_bias_gelu, C.byref(ti), C.byref(tw),
+                                C.byref(tb), C.byref(to), s)
+            else:
+                sA, sB = (1.0, 1.0) if scales is None else (float(scales[0]), float(scales[1]))
+                st = _auto_init(_L.tensorfuse_b200_gemm_fp8, x.data_ptr(), w.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                M, N, K, sA, sB, int(_torch_dt(b)), int(_torch_dt(out)), s)
         else:
             if out is None:
                 out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=x.dtype, device=x.device)

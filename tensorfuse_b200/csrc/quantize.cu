@@ -49,7 +49,17 @@ __global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, lo
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const long long n8 = vec ? n / 8 : 0;
-  for (long long u = tid; u < n8; u += nthreads) {
+  long long u = tid;
+  for (; u + 3 * nthreads < n8; u += 4 * nthreads) {      // four independent 16/32-byte loads in flight
+    float v[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) Vec8<T>::load(x + (u + j * nthreads) * 8, v[j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[j][i]));
+  }
+  for (; u < n8; u += nthreads) {
     float v[8];
     Vec8<T>::load(x + u * 8, v);
 #pragma unroll
@@ -87,16 +97,27 @@ __global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ x, 
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const long long n8 = vec ? n / 8 : 0;
-  for (long long u = tid; u < n8; u += nthreads) {
-    float v[8];
-    Vec8<T>::load(x + u * 8, v);
+  auto convert = [&](const float (&v)[8], long long unit) {
     uint32_t lo = 0, hi = 0;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       lo |= (uint32_t)(quant1(v[i], s) & 0xFF) << (8 * i);
       hi |= (uint32_t)(quant1(v[4 + i], s) & 0xFF) << (8 * i);
     }
-    *reinterpret_cast<uint2*>(q + u * 8) = make_uint2(lo, hi);
+    *reinterpret_cast<uint2*>(q + unit * 8) = make_uint2(lo, hi);
+  };
+  long long u = tid;
+  for (; u + 3 * nthreads < n8; u += 4 * nthreads) {
+    float v[4][8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) Vec8<T>::load(x + (u + j * nthreads) * 8, v[j]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) convert(v[j], u + j * nthreads);
+  }
+  for (; u < n8; u += nthreads) {
+    float v[8];
+    Vec8<T>::load(x + u * 8, v);
+    convert(v, u);
   }
   for (long long i = n8 * 8 + tid; i < n; i += nthreads) q[i] = (int8_t)quant1(widen<T>(x[i]), s);
 }
@@ -112,7 +133,7 @@ template <typename T>
 LaunchResult run(const void* x, long long n, int8_t* q, float* scale_dev, cudaStream_t stream) {
   const bool vec = (((uintptr_t)x & 15u) == 0) && (((uintptr_t)q & 7u) == 0);
   long long blocks = (n / 8 + 255) / 256;
-  const long long cap = 8ll * sm_count_now();
+  const long long cap = 16ll * sm_count_now();
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   if (cudaMemsetAsync(scale_dev, 0, sizeof(float), stream) != cudaSuccess) return kCudaError;
