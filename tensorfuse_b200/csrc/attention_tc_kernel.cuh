@@ -5,7 +5,7 @@
 // operator and leaves it empty: reference src/tensorfuse_c_api.cpp:288-311.)
 //
 // A work item is 128 query rows of one head; its keys are walked in blocks of
-// 128.  The kernel is persistent: two CTAs per SM (112 KB of shared memory, 256
+// 128.  The kernel is persistent: two CTAs per SM (96 KB of shared memory, 256
 // TMEM columns each) take work items round-robin, so TMEM allocation, barrier
 // set-up and descriptor fetches happen once, the next item's Q, K, V arrive and
 // its first scores are computed while the current item's output rows are
@@ -16,20 +16,22 @@
 //                      sequence / head strides, zero fill past the sequence end).
 //   warp 1, one lane : tcgen05.mma issuer.  S = Q K_j^T (M 128, N 128, K 64: both
 //                      operands K-major) into TMEM columns 0..127; O += P_j V_j
-//                      (M 128, N 64, K 128: P K-major from shared memory, V as
-//                      stored, i.e. MN-major) into columns 128..191.  S_{j+1} is
+//                      (M 128, N 64, K 128: P read from TMEM columns 192..255,
+//                      V as stored, i.e. MN-major) into columns 128..191.  S_{j+1} is
 //                      issued as soon as the softmax warps have read S_j.
 //   warps 2-5        : softmax.  Thread = query row = TMEM lane, so row maxima
 //                      and sums need no shuffles.  Pass 1 reads the 128 scores
 //                      of the row for the block maximum; pass 2 reads them again,
 //                      exponentiates in the base-2 domain (scale * log2 e folded
 //                      into one FMA), applies the dropout decisions, and writes
-//                      FP16 probabilities to the swizzled P tile.  When the
+//                      the FP16 probabilities back to TMEM (tcgen05.st), from
+//                      where the second product reads them as its A operand:
+//                      they never touch shared memory.  When the
 //                      running maximum moves, the same thread rescales its O row
 //                      in TMEM (tcgen05.ld / st) before releasing P to the MMA
 //                      issuer.  The final O row is divided by the row sum, scaled
-//                      by 1/(1-p), converted, staged in the (then idle) P tile and
-//                      stored through TMA.
+//                      by 1/(1-p), converted, staged in a 16 KB box and stored
+//                      through TMA.
 // Every mbarrier wait is bounded (ptx.cuh): an expired wait raises the CTA abort
 // flag, records a code in the watchdog word, and all roles fall through to the
 // tear-down that frees TMEM.
@@ -51,12 +53,12 @@ constexpr int KV_STAGES = 2;
 constexpr int TILE_BYTES = 128 * 128;          // 128 rows of 64 FP16
 constexpr int NUM_THREADS = 192;
 constexpr int SOFTMAX_THREADS = 128;
-constexpr int TMEM_COLS = 256;                 // S: 0..127, O: 128..191
+constexpr int TMEM_COLS = 256;                 // S: 0..127, O: 128..191, P (FP16 pairs): 192..255
 constexpr int OFF_Q = 0;
 constexpr int OFF_K = OFF_Q + TILE_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * TILE_BYTES;
-constexpr int OFF_P = OFF_V + KV_STAGES * TILE_BYTES;   // two boxes: keys 0..63, 64..127
-constexpr int OFF_BAR = OFF_P + 2 * TILE_BYTES;
+constexpr int OFF_P = OFF_V + KV_STAGES * TILE_BYTES;   // staging box of the output rows
+constexpr int OFF_BAR = OFF_P + TILE_BYTES;
 // barriers: q_full, q_empty, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_free, p_full, o_done
 constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 5;   // + the softmax warps' own rendezvous
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
@@ -192,7 +194,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (elect_one()) {
       constexpr uint32_t IDESC_S = make_idesc_major(1u, 0u, 0u, 0u, BQ, BKV);   // Q, K: K-major
       constexpr uint32_t IDESC_O = make_idesc_major(1u, 0u, 0u, 1u, BQ, HD);    // P K-major, V MN-major
-      const uint32_t tS = tmem_base, tO = tmem_base + 128;
+      const uint32_t tS = tmem_base, tO = tmem_base + 128, tP = tmem_base + 192;
       // S = Q K^T of key block number gi (counted over the whole CTA)
       auto issue_s = [&](uint32_t gi, bool last_of_item) -> bool {
         const int s = gi % KV_STAGES;
@@ -250,9 +252,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < BKV / 16; ++kk)
-            tc_mma_f16(tO, make_smem_desc(sP + (kk >> 2) * TILE_BYTES + (kk & 3) * 32, 16, 1024),
-                       make_smem_desc(sV + s * TILE_BYTES + kk * 2048, TILE_BYTES, 1024), IDESC_O,
-                       (j | kk) != 0 ? 1u : 0u);
+            tc_mma_f16_ts(tO, tP + kk * 8, make_smem_desc(sV + s * TILE_BYTES + kk * 2048, TILE_BYTES, 1024),
+                          IDESC_O, (j | kk) != 0 ? 1u : 0u);
           tc_commit(bar_o_done);
           tc_commit(v_empty(s));
         }
@@ -263,10 +264,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int qtr = warp & 3;                 // TMEM lane quarter this warp may touch
     const int row = qtr * 32 + lane;          // tile row = TMEM lane
     const uint32_t tS = tmem_base + (static_cast<uint32_t>(qtr * 32) << 16);
-    const uint32_t tO = tS + 128;
+    const uint32_t tO = tS + 128, tP = tS + 192;
     const float sl2 = p.scale_log2;
     bool ok = true;
-    bool store_pending = false;               // a TMA store may still be reading the staging box (P box 0)
+    bool store_pending = false;               // a TMA store may still be reading the staging box
     uint32_t g = 0;                           // key blocks processed by this CTA so far
     uint32_t r[2][32];
     unsigned long long blk_row = 0;           // Philox block index of element (b, h, q0 + row, 0)
@@ -351,29 +352,24 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               }
             }
         }
+        uint32_t w[16];                       // 32 probabilities as FP16 pairs
 #pragma unroll
-        for (int gq = 0; gq < 4; ++gq) {      // 8 keys -> one 16-byte vector of P
-          uint32_t w[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int i = gq * 8 + 2 * k;
-            float e0 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i]), sl2, nm));
-            float e1 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i + 1]), sl2, nm));
-            if (TAIL) {
-              if (c * 32 + i >= valid) e0 = 0.0f;
-              if (c * 32 + i + 1 >= valid) e1 = 0.0f;
-            }
-            ls0 += e0; ls1 += e1;
-            const __half2 hh = __floats2half2_rn(e0, e1);
-            w[k] = *reinterpret_cast<const uint32_t*>(&hh);
-            if (DROP) w[k] &= km[gq][k];
+        for (int k = 0; k < 16; ++k) {
+          const int i = 2 * k;
+          float e0 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i]), sl2, nm));
+          float e1 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i + 1]), sl2, nm));
+          if (TAIL) {
+            if (c * 32 + i >= valid) e0 = 0.0f;
+            if (c * 32 + i + 1 >= valid) e1 = 0.0f;
           }
-          const int col = c * 32 + gq * 8;
-          const uint32_t addr = sP + (col >> 6) * TILE_BYTES + row * 128 + ((((col & 63) >> 3) ^ (row & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
-                       : "memory");
+          ls0 += e0; ls1 += e1;
+          const __half2 hh = __floats2half2_rn(e0, e1);
+          w[k] = *reinterpret_cast<const uint32_t*>(&hh);
+          if (DROP) w[k] &= km[k >> 2][k & 3];
         }
+        tmem_st_32x16(tP + c * 16, w);
       }
+      tmem_st_wait();
       return ls0 + ls1;
     };
 
@@ -403,7 +399,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         PROF(1);
         // P and O are still in use by the previous block's second MMA
         if (j > 0 && !wait_warp(bar_o_done, (g - 1) & 1u, kWdODone)) { ok = false; break; }
-        if (j == 0 && !staging_ready()) { ok = false; break; }
         tc_fence_after();
         PROF(2);
         const float ls = tail ? pass2(TrueT{}, valid, j, m_new) : pass2(FalseT{}, valid, j, m_new);
@@ -423,7 +418,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           tmem_st_wait();
         }
         PROF(4);
-        fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(bar_p_full);
       }
@@ -433,7 +427,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       PROF(5);
-      if (nblk == 0 && !staging_ready()) break;
+      if (!staging_ready()) break;
       const float inv = nblk > 0 && l_run > 0.0f ? p.keep_scale / l_run : 0.0f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -451,7 +445,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             const __half2 hh = __floats2half2_rn(__uint_as_float(r[0][i]) * inv, __uint_as_float(r[0][i + 1]) * inv);
             w[k] = *reinterpret_cast<const uint32_t*>(&hh);
           }
-          // P box 0 is free once the item's last P V has completed: it stages the output rows
           const uint32_t addr = sP + row * 128 + (((c * 4 + gq) ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
                        : "memory");
