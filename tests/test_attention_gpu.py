@@ -91,6 +91,21 @@ def test_attention_equals_composition_of_library_operators(tf):
     assert (probe[~dropped] > 0).float().mean() > 0.99
 
 
+@pytest.mark.parametrize("p", [0.0, 0.2])
+def test_attention_scores_that_grow_along_the_keys(tf, oracle, p):
+    """Later key blocks dominate earlier ones by far more than the slack the kernel
+    allows its reference maximum (2^8): the block-repeat / rescale path."""
+    B, S, H, hd = 2, 640, 2, 64
+    q, k, v = make_qkv(B, S, S, H, hd, np.float16, seed=9)
+    k[:, 128:256] *= 6.0          # second block: moderate growth (no repeat for most rows)
+    k[:, 256:384] *= 30.0         # third block: every row outgrows its reference maximum
+    k[:, 384:512] *= 0.1          # fourth block: far below it
+    k[:, 600:] *= 60.0            # tail block: grows again
+    out = tf.fused_multi_head_attention(dev(q), dev(k), dev(v), None, H, p, seed=21)
+    check_watchdog()
+    close(host(out), oracle.attention(q, k, v, H, p=p, seed=21), np.float16)
+
+
 def test_attention_key_lengths(tf, oracle):
     B, S, H, hd = 4, 300, 2, 64
     q, k, v = make_qkv(B, S, S, H, hd, np.float16, seed=3)
