@@ -405,6 +405,30 @@ def side_workloads(tf, L, dev, peaks, args):
     except Exception as e:
         out["int8_gemm_error"] = repr(e)
 
+    # --- fused multi-head attention, BERT-large attention shape (32 x 16 heads x 512 x 64), on a fused QKV buffer
+    try:
+        Bq, Sq, Hh, hd = 32, 512, 16, 64
+        sets = 3                                         # 3 x (100 MB QKV + 34 MB output) > L2
+        qkvs = [torch.randn((Bq, Sq, 3, Hh * hd), device=dev).half() for _ in range(sets)]
+        outs = [torch.empty((Bq, Sq, Hh * hd), dtype=torch.float16, device=dev) for _ in range(sets)]
+        ld = 3 * Hh * hd
+        flop = 4.0 * Bq * Hh * Sq * Sq * hd
+        for pd in (0.0, 0.1):
+            def fn(i, pd=pd):
+                t = qkvs[i % sets]
+                st = L.tensorfuse_b200_attention(t[:, :, 0].data_ptr(), t[:, :, 1].data_ptr(), t[:, :, 2].data_ptr(),
+                                                 outs[i % sets].data_ptr(), Bq, Sq, Sq, Hh, hd, ld, ld, ld, Hh * hd,
+                                                 0, 0, 0, 0, 0, 0, 0, 0, 1, 0.0, pd, 5 + i, None, sp)
+                assert st == 0
+            avg, best = timed(fn, steps)
+            out[f"fused_attention_fp16_p{pd}"] = {
+                "metric": "attention_forward_tflops", "value": flop / (avg * 1e-3) / 1e12, "unit": "TFLOPS",
+                "ms": avg, "ms_min": best,
+                "config": {"workload": "attention_32x16x512x64", "dropout": pd, "flop": "4*B*H*S*S*d"},
+                "note": "bounded by the exponent unit (16 ex2 per clock and SM), not by the tensor cores"}
+    except Exception as e:
+        out["fused_attention_error"] = repr(e)
+
     # --- context only: the vendor library on the headline shape (not the product path)
     try:
         sets = 4
