@@ -12,7 +12,11 @@
 
 #include <mutex>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "gemm_tc_kernel.cuh"
+#include "gemm_tc_pair_kernel.cuh"
 #include "tma_host.h"
 
 namespace tfb {
@@ -112,6 +116,63 @@ LaunchResult run(const GemmArgs& a, cudaStream_t stream) {
   return kOk;
 }
 
+// The CTA-pair form of the same kernel (gemm_tc_pair_kernel.cuh).
+template <int KIND, int EPI, typename TOut>
+LaunchResult run_pair(const GemmArgs& a, cudaStream_t stream) {
+  using namespace tc2;
+  constexpr int ES = KindTraits<KIND>::ES;
+  auto kernel = gemm_tc_pair_kernel<KIND, EPI, TOut>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return kCudaError;
+  static bool ready[64] = {};
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (!ready[dev]) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return kCudaError;
+      }
+      ready[dev] = true;
+    }
+  }
+  CUtensorMap ma, mb, mc;
+  if (!cached_map(MapKey{a.A, ES, a.M, a.K, TBM}, &ma) ||
+      !cached_map(MapKey{a.B, ES, a.K, a.N, 128 / ES}, &mb) ||
+      !cached_map(MapKey{a.C, (int)sizeof(TOut), a.M, a.N, 32}, &mc))
+    return kLaunchFailed;
+  const int tiles = ((a.M + 2 * TBM - 1) / (2 * TBM)) * ((a.N + TBN - 1) / TBN);
+  const int pairs_max = sm_count(dev) / 2;
+  const int pairs = tiles < pairs_max ? tiles : pairs_max;
+  EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev};
+  kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(ma, mb, mc, a.bias, a.bias_dtype, a.M, a.N, a.K, ep,
+                                                          watchdog_word());
+  count_launch();
+  if (cudaGetLastError() != cudaSuccess) return kLaunchFailed;
+  return kOk;
+}
+
+// Kernel form: the CTA-pair kernel whenever the problem has more than one
+// 128-row band (a pair tile is 256 rows), the single-CTA kernel otherwise.
+// TENSORFUSE_B200_GEMM_FORM = single | pair overrides the choice (for measurements).
+bool use_pair_form(const GemmArgs& a) {
+  static const int mode = [] {
+    const char* e = std::getenv("TENSORFUSE_B200_GEMM_FORM");
+    if (e && std::strcmp(e, "pair") == 0) return 1;
+    if (e && std::strcmp(e, "single") == 0) return 2;
+    return 0;
+  }();
+  if (mode == 1) return true;
+  if (mode == 2) return false;
+  return a.M > tc::TBM;
+}
+
+template <int KIND, int EPI, typename TOut>
+LaunchResult run_any(const GemmArgs& a, cudaStream_t stream) {
+  return use_pair_form(a) ? run_pair<KIND, EPI, TOut>(a, stream) : run<KIND, EPI, TOut>(a, stream);
+}
+
 }  // namespace
 
 bool gemm_tc_eligible(const GemmArgs& a) {
@@ -133,16 +194,16 @@ bool gemm_tc_eligible(const GemmArgs& a) {
 LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   if (!gemm_tc_eligible(a)) return kUnsupported;
   if (!a.bias && a.epilogue != kEpiI8Raw) return kInvalidArgument;
-  if (a.in_dtype == kF16 && a.epilogue == kEpiLinear) return run<0, kEpiLinear, __half>(a, stream);
-  if (a.in_dtype == kF16) return run<0, kEpiGelu, __half>(a, stream);
-  if (a.in_dtype == kBF16 && a.epilogue == kEpiLinear) return run<2, kEpiLinear, __nv_bfloat16>(a, stream);
-  if (a.in_dtype == kBF16) return run<2, kEpiGelu, __nv_bfloat16>(a, stream);
-  if (a.in_dtype == kFp8E4M3 && a.out_dtype == kF16) return run<3, kEpiI8Dequant, __half>(a, stream);
-  if (a.in_dtype == kFp8E4M3) return run<3, kEpiI8Dequant, float>(a, stream);
-  if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF16) return run<1, kEpiI8Dequant, __half>(a, stream);
-  if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF32) return run<1, kEpiI8Dequant, float>(a, stream);
-  if (a.epilogue == kEpiI8Legacy) return run<1, kEpiI8Legacy, float>(a, stream);
-  return run<1, kEpiI8Raw, int>(a, stream);
+  if (a.in_dtype == kF16 && a.epilogue == kEpiLinear) return run_any<0, kEpiLinear, __half>(a, stream);
+  if (a.in_dtype == kF16) return run_any<0, kEpiGelu, __half>(a, stream);
+  if (a.in_dtype == kBF16 && a.epilogue == kEpiLinear) return run_any<2, kEpiLinear, __nv_bfloat16>(a, stream);
+  if (a.in_dtype == kBF16) return run_any<2, kEpiGelu, __nv_bfloat16>(a, stream);
+  if (a.in_dtype == kFp8E4M3 && a.out_dtype == kF16) return run_any<3, kEpiI8Dequant, __half>(a, stream);
+  if (a.in_dtype == kFp8E4M3) return run_any<3, kEpiI8Dequant, float>(a, stream);
+  if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF16) return run_any<1, kEpiI8Dequant, __half>(a, stream);
+  if (a.epilogue == kEpiI8Dequant && a.out_dtype == kF32) return run_any<1, kEpiI8Dequant, float>(a, stream);
+  if (a.epilogue == kEpiI8Legacy) return run_any<1, kEpiI8Legacy, float>(a, stream);
+  return run_any<1, kEpiI8Raw, int>(a, stream);
 }
 
 LaunchResult launch_gemm(const GemmArgs& a, cudaStream_t stream) {
