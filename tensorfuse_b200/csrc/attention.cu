@@ -240,10 +240,3 @@ LaunchResult launch_attention(const AttnArgs& a, cudaStream_t stream) {
 
 }  // namespace tfb
 
-#ifdef TFB_ATTN_PROF
-extern "C" unsigned long long tensorfuse_b200_attn_prof(int i) {
-  unsigned long long v[16];
-  cudaMemcpyFromSymbol(v, tfb::attn::g_attn_prof, sizeof(v));
-  return v[i & 15];
-}
-#endif

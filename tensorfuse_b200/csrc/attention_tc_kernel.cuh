@@ -80,12 +80,6 @@ struct Params {
   uint32_t key[20];
 };
 
-#ifdef TFB_ATTN_PROF
-__device__ unsigned long long g_attn_prof[16];
-#define PROF(i) do { if (prof_on) { const long long t_now = clock64(); prof_acc[i] += t_now - t_last; t_last = t_now; } } while (0)
-#else
-#define PROF(i) do {} while (0)
-#endif
 struct TrueT { static constexpr bool value = true; };
 struct FalseT { static constexpr bool value = false; };
 __device__ __forceinline__ float max3(float a, float b, float c) {
@@ -395,12 +389,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       return ls0 + ls1;
     };
 
-#ifdef TFB_ATTN_PROF
-    const bool prof_on = blockIdx.x == 0 && threadIdx.x == 64;
-    long long prof_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-    long long t_last = clock64();
-    const long long t_begin = t_last;
-#endif
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
       int q0, h, b, kv_len;
       tile_coords(t, q0, h, b, kv_len);
@@ -409,24 +397,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                  (unsigned long long)p.seq_kv) >> 3;
       float m_run = -INFINITY, l_run = 0.0f;
       for (int j = 0; j < nblk && ok; ++j, ++g) {
-        PROF(9);
         if (!wait_warp(bar_s_full, g & 1u, kWdSFull)) { ok = false; break; }
         tc_fence_after();
-        PROF(0);
         const int valid = kv_len - j * BKV;     // columns of this block that are real keys
         const bool tail = valid < BKV;
         const float mx = tail ? pass1(TrueT{}, valid) : pass1(FalseT{}, valid);
         const float m_new = fmaxf(m_run, mx * sl2);
         const float alpha = ex2_approx(m_run - m_new);     // 0 on the first block
-        PROF(1);
         // P and O are still in use by the previous block's second MMA
         if (j > 0 && !wait_warp(bar_o_done, (g - 1) & 1u, kWdODone)) { ok = false; break; }
         tc_fence_after();
-        PROF(2);
         const float ls = tail ? pass2(TrueT{}, valid, j, m_new) : pass2(FalseT{}, valid, j, m_new);
         l_run = fmaf(l_run, alpha, ls);
         m_run = m_new;
-        PROF(3);
         // rescale the O row when the maximum of any row of this warp moved
         if (j > 0 && __any_sync(0xFFFFFFFFu, alpha != 1.0f)) {
 #pragma unroll
@@ -439,16 +422,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           tmem_st_wait();
         }
-        PROF(4);
         tc_fence_before();
         mbar_arrive(bar_p_full);
       }
-      PROF(9);
       // ---------------------------------------------------------- final O rows
       if (ok && nblk > 0) ok = wait_warp(bar_o_done, (g - 1) & 1u, kWdODone);
       if (!ok) break;
       tc_fence_after();
-      PROF(5);
       if (!staging_ready()) break;
       const float inv = nblk > 0 && l_run > 0.0f ? p.keep_scale / l_run : 0.0f;
 #pragma unroll
@@ -474,22 +454,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       fence_proxy_async_smem();
       tc_fence_before();                       // the O reads above precede the next item's first P V
-      PROF(6);
       if (!softmax_sync()) break;
       if (threadIdx.x == 64) {
         tma_store_4d(&tmO, sP, 0, q0, h, b);
         bulk_commit_group();
       }
       store_pending = true;
-      PROF(7);
     }
-#ifdef TFB_ATTN_PROF
-    if (prof_on) {
-      for (int i = 0; i < 10; ++i) g_attn_prof[i] = (unsigned long long)prof_acc[i];
-      g_attn_prof[10] = (unsigned long long)(clock64() - t_begin);
-      g_attn_prof[11] = g;
-    }
-#endif
     if (threadIdx.x == 64) bulk_wait_group0();
   }
 

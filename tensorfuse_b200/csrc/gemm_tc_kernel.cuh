@@ -8,7 +8,7 @@
 //   * warp 0 (one elected lane): TMA producer.  Per K step (128 bytes of K) it
 //     loads a 128-row A box and the 256-column slab of B into a 4-deep ring of
 //     128-byte-swizzled shared-memory stages; completion is counted in bytes on
-//     an mbarrier.  Plain per-CTA loads, no multicast.
+//     an mbarrier.  Plain per-CTA loads.
 //   * warp 1 (one elected lane): issues tcgen05.mma (M 128, N 256, 32 bytes of K
 //     per instruction) from shared-memory descriptors into TMEM; tcgen05.commit
 //     frees the stage and, after the last K step, publishes the accumulator.
@@ -24,13 +24,14 @@
 //   A is [M,K] row-major -> K-major operand.  B is [K,N] row-major -> the
 //   "MN-major" operand form, consumed as stored: no transpose pass, no copy.
 //
-// Measured alternatives that are not kept: a two-CTA (cta_group::2, 256 x 256
-// pair tile, each CTA loading its own half of B) form of this kernel passed the
-// same tests but ran at 745 TFLOPS against 1204 TFLOPS for this one on the
-// 16384 x 4096 x 1024 FP16 problem (1660 against 2870 TOPS on the INT8 one),
-// whatever the stage count, the epilogue or the major-ness of B; TMA prefetches
-// of the next tile's operands into L2 cost 10-25 %; an evict-first hint on the
-// output stores and narrower rasterisation panels changed nothing.
+// This single-CTA form serves problems with one 128-row band; larger ones take
+// the CTA-pair form (gemm_tc_pair_kernel.cuh), which moves a third less through
+// each SM's shared memory: 1330 against 1215 TFLOPS on the 16384 x 4096 x 1024
+// FP16 problem, 3090 against 2780 TOPS on the INT8 one.  Measured alternatives
+// that are not kept: TMA prefetches of the next tile's operands into L2 cost
+// 10-25 %; an evict-first hint on the output stores and narrower rasterisation
+// panels changed nothing; register-to-global stores instead of the staged TMA
+// stores were slower (1083 TFLOPS in the pair form).
 //
 // Every mbarrier wait is bounded (ptx.cuh); a wait that expires raises a CTA
 // abort flag, records a code in the watchdog word and all roles fall through to

@@ -11,7 +11,8 @@
 // shared-memory port carries operand reads and TMA writes together).
 //   * both CTAs : warp 0 (one lane) TMA producer for its own operand halves,
 //                 byte counts signalled on the LEADER's "full" barrier
-//                 (cp.async.bulk.tensor ... .cta_group::2, no multicast);
+//                 (the cta_group::2 form of the tensor load; every load is
+//                 addressed to one CTA's shared memory only);
 //                 warps 2-9 epilogue of their own 128 x 256 accumulator, as in
 //                 the single-CTA kernel (same code).
 //   * leader    : warp 1 (one lane) issues the MMAs and commits to the "empty"
