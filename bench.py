@@ -35,7 +35,7 @@ M, K, N = 16384, 1024, 4096
 FLOP_PER_STEP = 2.0 * M * N * K
 NOMINAL = {"fp16_tflops": 2250.0, "int8_tops": 4500.0, "hbm_gbs": 8000.0}
 # DRAM bytes (read + write) of one launch, from the ncu captures summarised under profiles/.
-NCU_TRAFFIC = {"gemm_fp16": 120.2e6, "gemm_int8": 431.8e6, "softmax_p0": 620.7e6, "softmax_p0.1": 618.1e6}
+NCU_TRAFFIC = {"gemm_fp16": 121.2e6, "gemm_int8": 440.1e6, "softmax_p0": 620.7e6, "softmax_p0.1": 618.1e6}
 
 
 def measured_peaks():
@@ -306,7 +306,7 @@ def run_gpu(args):
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": achieved / peaks["tflops"], "traffic": NCU_TRAFFIC["gemm_fp16"],
                      "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch, "
-                                       "profiles/gemm_tc_kernel_gemm_fp16.md (algorithmic minimum 176.2 MB; part "
+                                       "profiles/gemm_tc_pair_kernel_gemm_fp16.md (algorithmic minimum 176.2 MB; part "
                                        "of the 134 MB output is still dirty in L2 when the kernel ends)",
                      "peak_source": f"{peaks['source']} bf16 cuBLAS burst (MEASURED_PEAKS.json)",
                      "frac_of_nominal_2250": achieved / NOMINAL["fp16_tflops"],
