@@ -119,6 +119,21 @@ TensorFuseStatus tensorfuse_b200_attention(const void* q, const void* k, const v
                                            float scale, float dropout_prob, unsigned long long seed,
                                            const int* kv_lengths, cudaStream_t stream);
 
+/* softmax(scale * x) + dropout over rows of `row_len` with the key positions
+ * >= kv_lengths[b] of batch item b masked inside the kernel (no -inf scores
+ * have to be materialised by the caller): input/output/mask are
+ * [batch, rows_per_item, row_len] (for attention probabilities rows_per_item =
+ * heads * seq_q), kv_lengths is a device array of `batch` ints or NULL, scale
+ * > 0.  A row with no valid position yields zeros.  Same Philox stream as
+ * tensorfuse_fused_softmax_dropout; FP32 arithmetic for both storage types.
+ * No reference counterpart: the reference's operator takes neither a scale nor
+ * a mask (src/tensorfuse/tensorfuse.h:72-88). */
+TensorFuseStatus tensorfuse_b200_softmax_dropout_masked(const void* input, void* output,
+                                                        unsigned char* dropout_mask, long long batch,
+                                                        long long rows_per_item, int row_len, int dtype,
+                                                        float scale, const int* kv_lengths, float dropout_prob,
+                                                        unsigned long long seed, cudaStream_t stream);
+
 /* Per-tensor symmetric INT8 quantisation of n FP16 / FP32 elements on the
  * device: *scale_dev = max|x| / 127 (1 for an all-zero tensor), q[i] =
  * clip(rint(x[i] / scale), -127, 127).  The scale stays in device memory, which

@@ -387,6 +387,42 @@ void tfo_softmax_dropout_exact(const void* in, void* out, uint8_t* mask, long ro
   }
 }
 
+/* Extended form of the library's softmax+dropout: softmax(scale * x) with the
+ * columns >= lengths[item] masked (item = row / rows_per_item; lengths may be
+ * NULL).  Widen, multiply by scale in FP32, mask, then the FP32-storage
+ * arithmetic of softmax_row_exact for both storage types. */
+void tfo_softmax_dropout_exact_ext(const void* in, void* out, uint8_t* mask, long rows, int L, int dtype,
+                                   float p, uint64_t seed, int vec, int warps, float scale,
+                                   const int* lengths, long rows_per_item, int threads) {
+  set_threads(threads);
+  const uint32_t thr = tfo_dropout_threshold(p);
+  const float ks = keep_scale_of(p);
+#pragma omp parallel
+  {
+    float* x = (float*)malloc(sizeof(float) * (size_t)L);
+    float* y = (float*)malloc(sizeof(float) * (size_t)L);
+#pragma omp for schedule(static)
+    for (long r = 0; r < rows; ++r) {
+      int len = L;
+      if (lengths) { len = lengths[r / rows_per_item]; if (len > L) len = L; if (len < 0) len = 0; }
+      for (int j = 0; j < L; ++j) {
+        const float v = dtype == 1 ? h2f(((const uint16_t*)in)[r * L + j]) : ((const float*)in)[r * L + j];
+        x[j] = j < len ? v * scale : -INFINITY;
+      }
+      softmax_row_exact(x, y, L, vec, warps, ks, 0);
+      for (int j = 0; j < L; ++j) {
+        uint64_t idx = (uint64_t)r * (uint64_t)L + (uint64_t)j;
+        int keep = thr == 0 ? 1 : dropout_keep(idx, seed, thr);
+        float v = keep ? y[j] : 0.0f;
+        mask[r * L + j] = (uint8_t)keep;
+        if (dtype == 1) ((uint16_t*)out)[r * L + j] = f2h(v);
+        else ((float*)out)[r * L + j] = v;
+      }
+    }
+    free(x); free(y);
+  }
+}
+
 /* ---------------------------------------------------------------- helpers */
 
 /* ------------------------------------------------- multi-head attention

@@ -59,6 +59,7 @@ def lib():
         L.tfo_dropout_threshold.argtypes = [f]
         L.tfo_dropout_mask.argtypes = [vp, u64, l, f, u64]
         L.tfo_softmax_dropout_exact.argtypes = [vp, vp, vp, l, i, i, f, u64, u64, i, i, i]
+        L.tfo_softmax_dropout_exact_ext.argtypes = [vp, vp, vp, l, i, i, f, u64, i, i, f, vp, l, i]
         L.tfo_attention_f32.argtypes = [vp, vp, vp, vp, i, i, i, i, i, f, f, u64, vp, i]
         _lib = L
     return _lib
@@ -172,6 +173,23 @@ def softmax_dropout_exact(x, p=0.0, seed=0, first_row=0, vec=8, warps=1, threads
     lib().tfo_softmax_dropout_exact(_p(x), _p(out), _p(mask), x.size // L, L,
                                     1 if x.dtype == np.float16 else 0, p, seed, first_row,
                                     vec, warps, threads)
+    return out, mask
+
+
+def softmax_dropout_masked_exact(x, scale=1.0, lengths=None, p=0.0, seed=0, vec=8, warps=1, threads=0):
+    """Bit-reproducible restatement of tensorfuse_b200_softmax_dropout_masked:
+    x is [batch, ..., L]; softmax(scale * x) over the last axis with the positions
+    >= lengths[b] of batch item b masked, then dropout."""
+    assert x.dtype in (np.float16, np.float32)
+    x = np.ascontiguousarray(x)
+    L = x.shape[-1]
+    rows = x.size // L
+    out = np.empty_like(x)
+    mask = np.empty(x.shape, np.uint8)
+    lens = None if lengths is None else np.ascontiguousarray(lengths, np.int32)
+    lib().tfo_softmax_dropout_exact_ext(_p(x), _p(out), _p(mask), rows, L, 1 if x.dtype == np.float16 else 0,
+                                        float(p), int(seed), vec, warps, float(scale),
+                                        None if lens is None else _p(lens), rows // x.shape[0], threads)
     return out, mask
 
 

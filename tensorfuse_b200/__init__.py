@@ -438,6 +438,39 @@ def fused_softmax_dropout(input, output=None, dropout_mask=None, dropout_prob=0.
     return output, dropout_mask
 
 
+def fused_softmax_dropout_masked(input, scale=1.0, kv_lengths=None, dropout_prob=0.0, output=None,
+                                 dropout_mask=None, stream=None, *, seed=None):
+    """dropout(softmax(scale * input, axis=-1)) with the key positions >=
+    kv_lengths[b] of batch item b masked inside the kernel.  ``input`` is a torch
+    CUDA tensor [batch, ..., L] (FP16 or FP32); ``kv_lengths`` one int per batch
+    item (tensor, array or None).  Returns ``(output, dropout_mask)``.  Extension
+    (tensorfuse_b200_softmax_dropout_masked): the reference's operator has neither
+    a scale nor a mask argument, callers add -inf to the scores beforehand."""
+    import torch
+    x = input.contiguous()
+    if output is None:
+        output = torch.empty_like(x)
+    if dropout_mask is None:
+        dropout_mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    lens_ptr = None
+    if kv_lengths is not None:
+        kv_lengths = torch.as_tensor(kv_lengths, dtype=torch.int32, device=x.device).contiguous()
+        if kv_lengths.numel() != x.shape[0]:
+            raise RuntimeError("fused_softmax_dropout_masked failed: " + get_error_string(Status.INVALID_TENSOR_SHAPE))
+        lens_ptr = kv_lengths.data_ptr()
+    if seed is None:
+        seed = _next_host_seed()
+    L = x.shape[-1]
+    batch = x.shape[0]
+    rows_per_item = x.numel() // max(1, batch * L)
+    with torch.cuda.device(x.device):
+        st = _auto_init(_L.tensorfuse_b200_softmax_dropout_masked, x.data_ptr(), output.data_ptr(),
+                        dropout_mask.data_ptr(), batch, rows_per_item, L, int(_torch_dt(x)), float(scale), lens_ptr,
+                        float(dropout_prob), int(seed) & 0xFFFFFFFFFFFFFFFF, _torch_stream(stream, x.device))
+    _check("fused_softmax_dropout_masked", st)
+    return output, dropout_mask
+
+
 def _softmax_torch_cuda(x, out, mask, p, stream, seed):
     import torch
     x = x.contiguous()
@@ -614,7 +647,7 @@ def is_gpu_supported() -> bool:
 
 __all__ = ["Status", "DataType", "Config", "TensorFuseStatus", "TensorFuseDataType",
            "TensorFuseConfig", "init", "shutdown", "cleanup", "get_version", "get_error_string",
-           "fused_gemm_bias_gelu", "fused_softmax_dropout", "fused_multi_head_attention", "fused_transformer_layer", "add_layernorm", "quantize_int8",
+           "fused_gemm_bias_gelu", "fused_softmax_dropout", "fused_softmax_dropout_masked", "fused_multi_head_attention", "fused_transformer_layer", "add_layernorm", "quantize_int8",
            "set_random_seed", "device_ids", "watchdog_status", "launch_count", "softmax_schedule",
            "plan_shards", "pinned_empty", "is_gpu_supported", "INT8_DEQUANT", "INT8_LEGACY",
            "INT8_RAW", "TENSORFUSE_MAX_DIMS"]

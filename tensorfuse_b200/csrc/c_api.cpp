@@ -442,6 +442,19 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_rows(const void* input, void* o
                                           dropout_prob, seed, first_row, stream));
 }
 
+TensorFuseStatus tensorfuse_b200_softmax_dropout_masked(const void* input, void* output, unsigned char* dropout_mask,
+                                                      long long batch, long long rows_per_item, int row_len,
+                                                      int dtype, float scale, const int* kv_lengths,
+                                                      float dropout_prob, unsigned long long seed,
+                                                      cudaStream_t stream) {
+  if (!input || !output || !dropout_mask) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  if (batch < 0 || rows_per_item <= 0 || row_len < 0) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
+  if (!(scale > 0.0f)) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  OwnerGuard og(output);
+  return to_status(launch_softmax_dropout_ext(input, output, dropout_mask, batch * rows_per_item, row_len, dtype,
+                                              dropout_prob, seed, 0, scale, kv_lengths, rows_per_item, true, stream));
+}
+
 TensorFuseStatus tensorfuse_b200_gemm_bias_act(const void* A, const void* B, const void* bias, void* C, int M,
                                              int N, int K, int dtype, int activation, float alpha, float beta,
                                              cudaStream_t stream) {

@@ -36,6 +36,14 @@ LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* ma
                                     unsigned long long seed, unsigned long long first_row,
                                     cudaStream_t stream);
 
+// Extended form: softmax(scale * x) with the columns >= lengths[item] of every
+// row masked (item = (first_row + row) / rows_per_item; lengths may be null).
+// Both storage types use the FP32-storage arithmetic here.
+LaunchResult launch_softmax_dropout_ext(const void* in, void* out, unsigned char* mask, long long rows, int L,
+                                        int dtype, float p, unsigned long long seed, unsigned long long first_row,
+                                        float scale, const int* lengths, long long rows_per_item, bool extended,
+                                        cudaStream_t stream);
+
 // ------------------------------------------------------ GEMM + bias + GELU
 enum Epilogue : int {
   kEpiGelu = 0,        // out = gelu(alpha*acc + beta*bias)                 (FP32 / FP16 paths)

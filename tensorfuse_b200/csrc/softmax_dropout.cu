@@ -50,7 +50,36 @@ struct SmParams {
   int hcmp;                      // thr <= 0x7C00: 15-bit fields order like positive FP16 numbers
   unsigned long long first_row;  // row offset of this shard inside the whole tensor
   uint32_t key[20];              // Philox round keys
+  // extended form (scores scaled and key-length masked on load); unused otherwise
+  float scale;                   // softmax(scale * x)
+  const int* lengths;            // valid row length per batch item, or null
+  long long rows_per_item;       // rows that share one entry of `lengths`
 };
+
+// Extended form: x <- scale * x for columns below the valid length, -inf from
+// there on.  The arithmetic that follows is the FP32-storage one whatever the
+// storage type, so that one CPU restatement covers both.
+template <bool EXT>
+__device__ __forceinline__ void adjust8(float (&x)[8], int col0, int len, float scale) {
+  if constexpr (EXT) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = (col0 + i < len) ? __fmul_rn(x[i], scale) : -INFINITY;
+  }
+}
+template <bool EXT>
+__device__ __forceinline__ float adjust1(float x, int col, int len, float scale) {
+  if constexpr (EXT) return col < len ? __fmul_rn(x, scale) : -INFINITY;
+  return x;
+}
+template <bool EXT>
+__device__ __forceinline__ int valid_length(const SmParams& p, long long row) {
+  if constexpr (EXT) {
+    if (p.lengths == nullptr) return p.L;
+    const long long b = (long long)((p.first_row + (unsigned long long)row) / (unsigned long long)p.rows_per_item);
+    return max(0, min(p.L, p.lengths[b]));
+  }
+  return p.L;
+}
 
 constexpr float kLog2e = 0x1.715476p+0f;
 constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
@@ -244,9 +273,9 @@ __device__ __forceinline__ uint32_t hmax2_bits(uint32_t a, uint32_t b) {
 // over rows, next row's loads in flight while the current row is processed.
 // FP16 storage keeps the row packed for as long as possible: the maximum and
 // the clamp at lo are taken on half2 words, the widening to FP32 happens once.
-template <typename T, int CH, bool DROP>
+template <typename T, int CH, bool DROP, bool EXT>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
-  constexpr bool HF = sizeof(T) == 2;
+  constexpr bool HF = sizeof(T) == 2 && !EXT;
   const int lane = threadIdx.x & 31;
   const int L = p.L;
   const long long stride = (long long)gridDim.x * 8;
@@ -274,6 +303,7 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
       else nxt[c].fill_neg_inf();
     }
 
+    const int len = valid_length<EXT>(p, row);
     float m;
     if constexpr (HF) {
       uint32_t m2 = 0xFC00FC00u;
@@ -292,6 +322,7 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
       for (int c = 0; c < CH; ++c) {
         float x[8];
         cur[c].widen(x);
+        adjust8<EXT>(x, (lane + 32 * c) * 8, len, p.scale);
 #pragma unroll
         for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
       }
@@ -320,6 +351,7 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
       } else {
         float x[8];
         cur[c].widen(x);
+        adjust8<EXT>(x, (lane + 32 * c) * 8, len, p.scale);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           e2[c][k] = exp_pair<false>(x[2 * k], x[2 * k + 1], ctx);
@@ -349,9 +381,9 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
 // -------------------------------------------------------- CTA-per-row kernel
 // Three passes over the row (the second and third are served by L2).  VEC = 8
 // needs 16-byte aligned rows and L % 8 == 0; VEC = 1 takes anything.
-template <typename T, int VEC, bool DROP>
+template <typename T, int VEC, bool DROP, bool EXT>
 __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
-  constexpr bool HF = sizeof(T) == 2;
+  constexpr bool HF = sizeof(T) == 2 && !EXT;
   __shared__ float red[32];
   const int tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31, warp = tid >> 5;
   const int nwarps = nthr >> 5;
@@ -362,16 +394,18 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
 
   for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
     const T* xr = in + row * L;
+    const int len = valid_length<EXT>(p, row);
     // pass 1: maximum
     float m = -INFINITY;
     for (int u = tid; u < units; u += nthr) {
       if constexpr (VEC == 8) {
         Unit<T> un; un.load(xr + u * 8);
         float x[8]; un.widen(x);
+        adjust8<EXT>(x, u * 8, len, p.scale);
 #pragma unroll
         for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
       } else {
-        m = fmaxf(m, (float)xr[u]);
+        m = fmaxf(m, adjust1<EXT>((float)xr[u], u, len, p.scale));
       }
     }
     m = warp_max(m);
@@ -391,6 +425,7 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
       for (int u = tid; u < units; u += nthr) {
         Unit<T> un; un.load(xr + u * 8);
         float x[8]; un.widen(x);
+        adjust8<EXT>(x, u * 8, len, p.scale);
 #pragma unroll
         for (int k = 0; k < 4; ++k) s2 = add2(s2, exp_pair<HF>(x[2 * k], x[2 * k + 1], ctx));
       }
@@ -399,7 +434,7 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
     } else {
       float s0 = 0.0f;
       for (int u = tid; u < units; u += nthr) {
-        const float xv = (float)xr[u];
+        const float xv = adjust1<EXT>((float)xr[u], u, len, p.scale);
         s0 = __fadd_rn(s0, unpack2(exp_pair<HF>(xv, xv, ctx)).x);
       }
       lane_sum = __fadd_rn(s0, 0.0f);
@@ -420,13 +455,14 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
       if constexpr (VEC == 8) {
         Unit<T> un; un.load(xr + u * 8);
         float x[8]; un.widen(x);
+        adjust8<EXT>(x, u * 8, len, p.scale);
         uint64_t e2[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) e2[k] = exp_pair<HF>(x[2 * k], x[2 * k + 1], ctx);
         const long long off = row * L + (long long)u * 8;
         finish_unit<T, DROP>(e2, g2, out + off, p.mask + off, p, (idx0 >> 3) + (unsigned)u);
       } else {
-        const float xv = (float)xr[u];
+        const float xv = adjust1<EXT>((float)xr[u], u, len, p.scale);
         const float e = unpack2(exp_pair<HF>(xv, xv, ctx)).x;
         float y = __fmul_rn(e, g);
         unsigned keep = 1u;
@@ -447,38 +483,51 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
   }
 }
 
-template <typename T, int CH>
-void launch_warp(const SmParams& p, bool drop, int sms, cudaStream_t stream) {
+template <typename T, int CH, bool DROP, bool EXT>
+void launch_warp_t(const SmParams& p, int sms, cudaStream_t stream) {
   const long long ctas_needed = (p.rows + 7) / 8;
   int per_sm = 0;
-  if (drop) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, softmax_warp_kernel<T, CH, true>, 256, 0);
-  else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, softmax_warp_kernel<T, CH, false>, 256, 0);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, softmax_warp_kernel<T, CH, DROP, EXT>, 256, 0);
   if (per_sm < 1) per_sm = 1;
   const long long cap = (long long)sms * per_sm;
   const int grid = (int)(ctas_needed < cap ? ctas_needed : cap);
-  if (drop) softmax_warp_kernel<T, CH, true><<<grid, 256, 0, stream>>>(p);
-  else softmax_warp_kernel<T, CH, false><<<grid, 256, 0, stream>>>(p);
+  softmax_warp_kernel<T, CH, DROP, EXT><<<grid, 256, 0, stream>>>(p);
+}
+template <typename T, int CH>
+void launch_warp(const SmParams& p, bool drop, bool ext, int sms, cudaStream_t stream) {
+  if (ext) {
+    if (drop) launch_warp_t<T, CH, true, true>(p, sms, stream);
+    else launch_warp_t<T, CH, false, true>(p, sms, stream);
+  } else {
+    if (drop) launch_warp_t<T, CH, true, false>(p, sms, stream);
+    else launch_warp_t<T, CH, false, false>(p, sms, stream);
+  }
 }
 
 template <typename T, int VEC>
-void launch_block(const SmParams& p, bool drop, int warps, int sms, cudaStream_t stream) {
+void launch_block(const SmParams& p, bool drop, bool ext, int warps, int sms, cudaStream_t stream) {
   const long long cap = (long long)sms * (warps == 1 ? 32 : 8);
   const int grid = (int)(p.rows < cap ? p.rows : cap);
-  if (drop) softmax_block_kernel<T, VEC, true><<<grid, 32 * warps, 0, stream>>>(p);
-  else softmax_block_kernel<T, VEC, false><<<grid, 32 * warps, 0, stream>>>(p);
+  if (ext) {
+    if (drop) softmax_block_kernel<T, VEC, true, true><<<grid, 32 * warps, 0, stream>>>(p);
+    else softmax_block_kernel<T, VEC, false, true><<<grid, 32 * warps, 0, stream>>>(p);
+  } else {
+    if (drop) softmax_block_kernel<T, VEC, true, false><<<grid, 32 * warps, 0, stream>>>(p);
+    else softmax_block_kernel<T, VEC, false, false><<<grid, 32 * warps, 0, stream>>>(p);
+  }
 }
 
 template <typename T>
-void dispatch(const SmParams& p, bool drop, SoftmaxSchedule sch, int sms, cudaStream_t stream) {
+void dispatch(const SmParams& p, bool drop, bool ext, SoftmaxSchedule sch, int sms, cudaStream_t stream) {
   if (sch.vec == 8 && sch.warps == 1) {
-    if (p.L <= 256) launch_warp<T, 1>(p, drop, sms, stream);
-    else if (p.L <= 512) launch_warp<T, 2>(p, drop, sms, stream);
-    else if (p.L <= 1024) launch_warp<T, 4>(p, drop, sms, stream);
-    else launch_warp<T, 8>(p, drop, sms, stream);
+    if (p.L <= 256) launch_warp<T, 1>(p, drop, ext, sms, stream);
+    else if (p.L <= 512) launch_warp<T, 2>(p, drop, ext, sms, stream);
+    else if (p.L <= 1024) launch_warp<T, 4>(p, drop, ext, sms, stream);
+    else launch_warp<T, 8>(p, drop, ext, sms, stream);
   } else if (sch.vec == 8) {
-    launch_block<T, 8>(p, drop, sch.warps, sms, stream);
+    launch_block<T, 8>(p, drop, ext, sch.warps, sms, stream);
   } else {
-    launch_block<T, 1>(p, drop, sch.warps, sms, stream);
+    launch_block<T, 1>(p, drop, ext, sch.warps, sms, stream);
   }
 }
 
@@ -514,7 +563,15 @@ LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* ma
                                     long long rows, int L, int dtype, float p,
                                     unsigned long long seed, unsigned long long first_row,
                                     cudaStream_t stream) {
+  return launch_softmax_dropout_ext(in, out, mask, rows, L, dtype, p, seed, first_row, 1.0f, nullptr, 0, false, stream);
+}
+
+LaunchResult launch_softmax_dropout_ext(const void* in, void* out, unsigned char* mask, long long rows, int L,
+                                        int dtype, float p, unsigned long long seed, unsigned long long first_row,
+                                        float scale, const int* lengths, long long rows_per_item, bool extended,
+                                        cudaStream_t stream) {
   if (!in || !out || !mask) return kInvalidArgument;
+  if (extended && (!(scale > 0.0f) || (lengths != nullptr && rows_per_item <= 0))) return kInvalidArgument;
   if (!(p >= 0.0f && p <= 1.0f)) return kInvalidArgument;
   if (dtype != kF16 && dtype != kF32) return kUnsupported;
   if (rows < 0 || L < 0) return kInvalidArgument;
@@ -528,13 +585,14 @@ LaunchResult launch_softmax_dropout(const void* in, void* out, unsigned char* ma
   sp.hcmp = sp.thr <= 0x7C00u ? 1 : 0;
   sp.first_row = first_row;
   philox_round_keys(seed, sp.key);
+  sp.scale = scale; sp.lengths = lengths; sp.rows_per_item = rows_per_item > 0 ? rows_per_item : 1;
   const bool drop = sp.thr != 0u;
   const uintptr_t bits = (uintptr_t)in | (uintptr_t)out | ((uintptr_t)mask << 1);
   const bool aligned16 = (bits & 15u) == 0;
   const SoftmaxSchedule sch = softmax_schedule(L, dtype, aligned16);
   const int sms = sm_count_of_current_device();
-  if (dtype == kF16) dispatch<__half>(sp, drop, sch, sms, stream);
-  else dispatch<float>(sp, drop, sch, sms, stream);
+  if (dtype == kF16) dispatch<__half>(sp, drop, extended, sch, sms, stream);
+  else dispatch<float>(sp, drop, extended, sch, sms, stream);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? kOk : kCudaError;
 }
