@@ -170,7 +170,12 @@ bool use_pair_form(const GemmArgs& a) {
 
 template <int KIND, int EPI, typename TOut>
 LaunchResult run_any(const GemmArgs& a, cudaStream_t stream) {
-  return use_pair_form(a) ? run_pair<KIND, EPI, TOut>(a, stream) : run<KIND, EPI, TOut>(a, stream);
+  if (use_pair_form(a)) {
+    const LaunchResult r = run_pair<KIND, EPI, TOut>(a, stream);
+    if (r != kLaunchFailed) return r;
+    cudaGetLastError();   // e.g. a partition that cannot co-schedule two CTAs: the single-CTA form still can run
+  }
+  return run<KIND, EPI, TOut>(a, stream);
 }
 
 }  // namespace

@@ -165,12 +165,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    constexpr bool kIntAcc = KT::kIntAcc;
-    constexpr int CHUNKS_PER_BOX = sizeof(TOut) == 2 ? 2 : 1;   // a staging row is 128 bytes
-    constexpr int VEC_PER_CHUNK = sizeof(TOut) == 2 ? 4 : 8;    // 16-byte vectors per 32 columns
-    const int q = warp & 3;                  // TMEM lane quarter this warp may read
-    const int half = (warp - 2) >> 2;        // which 128 of the 256 columns
-    const int e = threadIdx.x - 64;          // 0..255
     const uint32_t staging = smem_u32(smem + P_OFF_STAGING) + (warp - 2) * STAGING_BYTES;
     const EpiParams ep = resolve_scales(ep_in);
     uint32_t t_local = 0;
@@ -178,57 +172,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const uint32_t buf = t_local & 1u, use = t_local >> 1;
       int tm, tn;
       tile_coords(tile, tiles_m2, tiles_n, tm, tn);
-      const int m0 = tm * 2 * TBM + (int)rank * TBM, n0 = tn * TBN;
-      float* bs = bias_s + buf * TBN;
-      if (EPI != kEpiI8Raw) {
-        const int n = n0 + e;
-        float bv = 0.0f;
-        if (n < N) bv = bias_dtype == kF16    ? __half2float(static_cast<const __half*>(bias)[n])
-                        : bias_dtype == kBF16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(bias)[n])
-                                              : static_cast<const float*>(bias)[n];
-        bs[e] = bv;
-      }
-      mbar_arrive(bias_bar(buf));
-      if (!mbar_wait(bias_bar(buf), use & 1u, abort_flag, status, kWdBias)) break;
-      if (!mbar_wait(tfull_bar(buf), use & 1u, abort_flag, status, kWdTmemFull)) break;
-      tc_fence_after();
-
-      const int row0 = m0 + q * 32;            // first row of this warp's 32-row band
-      const int nc = n0 + half * 128;          // first of this warp's 128 columns
-      const float* bsh = bs + half * 128;
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * TBN + half * 128;
       const uint32_t tempty_leader = map_to_cta(tempty_bar(buf), 0);
-      uint32_t acc[2][32];
-      tmem_ld_32x32(t_row, acc[0]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c < 3) tmem_ld_32x32(t_row + (c + 1) * 32, acc[(c + 1) & 1]);
-        else {
-          // every TMEM read of this accumulator is done: hand it back to the MMA issuer
-          tc_fence_before();
-          mbar_arrive_cluster(tempty_leader);
-        }
-        uint32_t w[32];
-        epilogue_chunk<EPI, TOut, kIntAcc>(acc[c & 1], bsh + c * 32, ep, w);
-        if (c % CHUNKS_PER_BOX == 0) {
-          if (lane == 0) bulk_wait_read_all();   // the previous box has left the staging buffer
-          __syncwarp();
-        }
-#pragma unroll
-        for (int g = 0; g < VEC_PER_CHUNK; ++g)
-          staging_store16(staging, lane, (c % CHUNKS_PER_BOX) * VEC_PER_CHUNK + g,
-                          make_uint4(w[4 * g], w[4 * g + 1], w[4 * g + 2], w[4 * g + 3]));
-        if (c % CHUNKS_PER_BOX == CHUNKS_PER_BOX - 1) {
-          fence_async_smem();
-          __syncwarp();
-          const int x = nc + (c / CHUNKS_PER_BOX) * (128 / (int)sizeof(TOut));
-          if (lane == 0 && x < N && row0 < M) {
-            tma_store_2d(&tmC, staging, x, row0);
-            bulk_commit();
-          }
-        }
-      }
+      if (!epilogue_tile<EPI, TOut, KT::kIntAcc>(&tmC, bias, bias_dtype, M, N, tm * 2 * TBM + (int)rank * TBM, tn * TBN,
+                                                 buf, use, bias_s, staging, bias_bar(buf), tfull_bar(buf), tmem_base, ep,
+                                                 abort_flag, status, [&] { mbar_arrive_cluster(tempty_leader); }))
+        break;
     }
     if (lane == 0) bulk_wait_all();
   }
