@@ -13,6 +13,7 @@
 // Staging buffers are grow-only and live until tensorfuse_shutdown.
 #include <algorithm>
 #include <thread>
+#include <utility>
 #include <vector>
 
 #include "kernels.h"
@@ -74,8 +75,17 @@ TensorFuseStatus gemm_shard(DeviceCtx* cx, const GemmHostJob& j, long long row0,
   DeviceGuard dg(cx->id);
   const size_t es = dtype_size(j.in_dtype), bs = dtype_size(j.bias_dtype), os = dtype_size(j.out_dtype);
   const size_t a_row = (size_t)j.K * es, c_row = (size_t)j.N * os;
+  // Chunks of about 16 MB of traffic, but the first ones are small (256 rows, doubling): the
+  // device -> host copy, which dominates, starts as soon as a sliver of the output exists.
   const long long chunk = rows_per_chunk(a_row + c_row, size_t(16) << 20, 128);
-  const size_t nchunks = (size_t)((rows + chunk - 1) / chunk);
+  std::vector<std::pair<long long, long long>> chunks;
+  for (long long r0 = 0, step = std::min<long long>(256, chunk); r0 < rows;) {
+    const long long nr = std::min<long long>(step, rows - r0);
+    chunks.emplace_back(r0, nr);
+    r0 += nr;
+    step = std::min<long long>(step * 2, chunk);
+  }
+  const size_t nchunks = chunks.size();
   CK(cx->ensure(nchunks));
   CK(cx->a.reserve((size_t)rows * a_row));
   CK(cx->c.reserve((size_t)rows * c_row));
@@ -88,8 +98,8 @@ TensorFuseStatus gemm_shard(DeviceCtx* cx, const GemmHostJob& j, long long row0,
   CK(cudaStreamWaitEvent(cx->s_compute, cx->ev_weights, 0));
 
   for (size_t i = 0; i < nchunks; ++i) {
-    const long long r0 = (long long)i * chunk;
-    const long long nr = std::min<long long>(chunk, rows - r0);
+    const long long r0 = chunks[i].first;
+    const long long nr = chunks[i].second;
     char* dA = static_cast<char*>(cx->a.ptr) + (size_t)r0 * a_row;
     char* dC = static_cast<char*>(cx->c.ptr) + (size_t)r0 * c_row;
     CK(cudaMemcpyAsync(dA, j.A + (size_t)(row0 + r0) * a_row, (size_t)nr * a_row,

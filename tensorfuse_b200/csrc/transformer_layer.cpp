@@ -10,7 +10,9 @@
 // returns success without touching the output (src/tensorfuse_c_api.cpp:313-329).
 // Workspace (4 x [tokens, hidden] + [tokens, ffn]) comes from the stream-ordered
 // allocator and is returned to it on the same stream, so the call stays
-// asynchronous and calls on different streams do not share buffers.
+// asynchronous and calls on different streams do not share buffers; the first
+// call on a device raises the release threshold of that device's default pool
+// so that the workspace stays cached between calls.
 #include <cuda_runtime.h>
 
 #include "kernels.h"
@@ -28,6 +30,22 @@ bool is_matrix(const TensorFuseTensor* t, int rows, int cols, TensorFuseDataType
 }
 bool is_vector(const TensorFuseTensor* t, int n, TensorFuseDataType dt) {
   return t && t->data && t->shape.ndims == 1 && t->shape.dims[0] == n && t->dtype == dt;
+}
+
+// The workspace comes from the device's default stream-ordered pool.  Left at its
+// default the pool hands freed memory back to the driver at the next
+// synchronisation and the following call pays for mapping it again (milliseconds
+// at BERT-large sizes); raising the release threshold once keeps it cached.
+void keep_pool_cached(int dev) {
+  static bool done[64] = {};
+  if (dev < 0 || dev >= 64 || done[dev]) return;
+  cudaMemPool_t pool = nullptr;
+  if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess && pool != nullptr) {
+    unsigned long long threshold = ~0ull;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold);
+  }
+  cudaGetLastError();
+  done[dev] = true;
 }
 
 LaunchResult gemm(const void* A, const void* B, const void* bias, void* C, int M, int N, int K, int dt, int epi,
@@ -83,7 +101,9 @@ extern "C" TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseT
   const int kdt = dt == TENSORFUSE_FLOAT16 ? kF16 : kF32;
   const size_t es = kdt == kF16 ? 2 : 4;
 
-  DeviceGuard guard(device_of_pointer(output->data));
+  const int dev = device_of_pointer(output->data);
+  DeviceGuard guard(dev);
+  keep_pool_cached(dev);
   auto round_up = [](size_t v) { return (v + 255) & ~(size_t)255; };
   const size_t mh = round_up((size_t)M * H * es), mf = round_up((size_t)M * F * es);
   const size_t zb = p->use_bias ? 0 : round_up((size_t)(H > F ? H : F) * es);
