@@ -152,6 +152,20 @@ TensorFuseStatus tensorfuse_b200_add_layernorm(const void* x, const void* residu
                                                const void* beta, void* out, long long rows, int hidden,
                                                int dtype, float eps, cudaStream_t stream);
 
+/* Channel-wise variant for weights w[K, N] (row-major FP16 / FP32): one scale per
+ * output column, scales_dev[n] = max_k |w[k,n]| / 127 (1 for an all-zero column),
+ * q[k,n] = clip(rint(w[k,n] / scales_dev[n]), -127, 127). */
+TensorFuseStatus tensorfuse_b200_quantize_int8_columns(const void* w, int dtype, int K, int N, signed char* q,
+                                                       float* scales_dev, cudaStream_t stream);
+
+/* INT8 GEMM with a per-tensor activation scale and per-column weight scales, both
+ * read on the device: C[m,n] = gelu(acc[m,n] * *scale_A_dev * scale_B_cols_dev[n] + bias[n]),
+ * FP16 or FP32 bias and output.  scale_A_dev may be NULL (= 1). */
+TensorFuseStatus tensorfuse_b200_gemm_int8_channelwise(const void* A, const void* B, const void* bias, void* C,
+                                                       int M, int N, int K, const float* scale_A_dev,
+                                                       const float* scale_B_cols_dev, int bias_dtype,
+                                                       int out_dtype, cudaStream_t stream);
+
 /* Row-sharded softmax+dropout: `rows` rows of length `row_len`; `first_row`
  * is the index of the first of them inside the whole tensor, so that a shard
  * draws exactly the dropout decisions it would get as part of the whole.

@@ -297,6 +297,15 @@ def quantize_sym_int8(x):
     return q, scale
 
 
+def quantize_sym_int8_columns(w):
+    """Channel-wise variant for a weight matrix [K, N]: one scale per column."""
+    w = np.asarray(w).astype(np.float32)
+    amax = np.max(np.abs(w), axis=0).astype(np.float32)
+    scales = np.where(amax > 0, amax / np.float32(127.0), np.float32(1.0)).astype(np.float32)
+    q = np.clip(np.rint(w / scales[None, :]), -127, 127).astype(np.int8)
+    return q, scales
+
+
 # -------------------------------------------------------------- numpy twins
 
 def np_gelu(x):

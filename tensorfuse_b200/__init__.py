@@ -350,7 +350,13 @@ def _gemm_torch_cuda(x, w, b, out, stream, scales, out_dtype, int8_mode):
                              torch.int32: INT8_RAW}[odt]
             if out is None:
                 out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=odt, device=x.device)
-            if scales is not None and _is_torch(scales[0]):
+            if scales is not None and _is_torch(scales[1]) and scales[1].numel() == N and N > 1:
+                # per-column weight scales (and a device-resident activation scale)
+                sa = scales[0] if _is_torch(scales[0]) else torch.tensor([float(scales[0])], device=x.device)
+                st = _auto_init(_L.tensorfuse_b200_gemm_int8_channelwise, x.data_ptr(), w.data_ptr(), b.data_ptr(),
+                                out.data_ptr(), M, N, K, sa.data_ptr(), scales[1].contiguous().data_ptr(),
+                                int(_torch_dt(b)), int(_torch_dt(out)), s)
+            elif scales is not None and _is_torch(scales[0]):
                 # device-resident scales: struct ABI, no host synchronisation
                 ti = _c_tensor(x.data_ptr(), (M, x.shape[-1]), in_dt, scales[0].data_ptr())
                 tw = _c_tensor(w.data_ptr(), (K, N), in_dt, scales[1].data_ptr())
@@ -617,17 +623,27 @@ def add_layernorm(x, residual, gamma, beta, eps=1e-12, output=None, stream=None)
     return output
 
 
-def quantize_int8(x, stream=None):
-    """Per-tensor symmetric INT8 quantisation of a torch CUDA tensor (FP16 or
-    FP32) on the device: returns ``(q, scale)`` with ``q`` int8 of x's shape and
-    ``scale`` a one-element FP32 CUDA tensor (= max|x|/127), ready to be passed
-    as a device scale to the INT8 GEMM.  No host synchronisation."""
+def quantize_int8(x, stream=None, *, per_column=False):
+    """Symmetric INT8 quantisation of a torch CUDA tensor (FP16 or FP32) on the
+    device: returns ``(q, scale)`` with ``q`` int8 of x's shape and ``scale`` a
+    one-element FP32 CUDA tensor (= max|x|/127), or, with ``per_column=True`` for
+    a weight matrix [K, N], N scales (one per output column).  Either is ready to
+    be passed as a device scale to the INT8 GEMM.  No host synchronisation."""
     import torch
     if not (_is_torch(x) and x.is_cuda):
         raise RuntimeError("quantize_int8 failed: " + get_error_string(Status.INVALID_ARGUMENT))
     x = x.contiguous()
     dt = _torch_dt(x)
     q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    if per_column:
+        if x.dim() != 2:
+            raise RuntimeError("quantize_int8 failed: " + get_error_string(Status.INVALID_TENSOR_SHAPE))
+        scales = torch.empty(x.shape[1], dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            st = _auto_init(_L.tensorfuse_b200_quantize_int8_columns, x.data_ptr(), int(dt), x.shape[0], x.shape[1],
+                            q.data_ptr(), scales.data_ptr(), _torch_stream(stream, x.device))
+        _check("quantize_int8", st)
+        return q, scales
     scale = torch.empty(1, dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         st = _auto_init(_L.tensorfuse_b200_quantize_int8, x.data_ptr(), int(dt), x.numel(), q.data_ptr(),

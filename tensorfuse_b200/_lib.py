@@ -91,6 +91,8 @@ def _load():
     sig("tensorfuse_b200_gemm_bias_act", i, [vp, vp, vp, vp, i, i, i, i, i, f, f, st])
     sig("tensorfuse_b200_softmax_dropout_masked", i, [vp, vp, vp, ll, ll, i, i, f, vp, f, ull, st])
     sig("tensorfuse_b200_add_layernorm", i, [vp, vp, vp, vp, vp, ll, i, i, f, st])
+    sig("tensorfuse_b200_quantize_int8_columns", i, [vp, i, i, i, vp, vp, st])
+    sig("tensorfuse_b200_gemm_int8_channelwise", i, [vp, vp, vp, vp, i, i, i, vp, vp, i, i, st])
     sig("tensorfuse_b200_quantize_int8", i, [vp, i, ll, vp, vp, st])
     sig("tensorfuse_b200_attention", i, [vp, vp, vp, vp, i, i, i, i, i] + [ll] * 12 + [i, f, f, ull, vp, st])
     sig("tensorfuse_b200_softmax_dropout_rows", i, [vp, vp, vp, ll, i, i, f, ull, ull, st])

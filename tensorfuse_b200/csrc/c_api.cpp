@@ -489,6 +489,32 @@ TensorFuseStatus tensorfuse_b200_attention(const void* q, const void* k, const v
   return to_status(launch_attention(a, stream));
 }
 
+TensorFuseStatus tensorfuse_b200_quantize_int8_columns(const void* w, int dtype, int K, int N, signed char* q,
+                                                     float* scales_dev, cudaStream_t stream) {
+  if (!w || !q || !scales_dev || K < 0 || N < 0) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  OwnerGuard og(q);
+  return to_status(launch_quantize_int8_columns(w, dtype, K, N, q, scales_dev, stream));
+}
+
+TensorFuseStatus tensorfuse_b200_gemm_int8_channelwise(const void* A, const void* B, const void* bias, void* C, int M,
+                                                     int N, int K, const float* scale_A_dev,
+                                                     const float* scale_B_cols_dev, int bias_dtype, int out_dtype,
+                                                     cudaStream_t stream) {
+  if (!A || !B || !C || !bias || !scale_B_cols_dev) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  if (M <= 0 || N <= 0 || K <= 0) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
+  if (out_dtype != kF16 && out_dtype != kF32) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  if (bias_dtype != kF16 && bias_dtype != kF32) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  GemmArgs a{};
+  a.A = A; a.B = B; a.bias = bias; a.C = C;
+  a.M = M; a.N = N; a.K = K;
+  a.in_dtype = kI8; a.bias_dtype = bias_dtype; a.out_dtype = out_dtype;
+  a.epilogue = kEpiI8Dequant;
+  a.alpha = 1.0f; a.beta = 1.0f; a.scale = 1.0f;
+  a.scale_a_dev = scale_A_dev; a.scale_b_dev = nullptr; a.scale_b_cols = scale_B_cols_dev;
+  OwnerGuard og(C);
+  return to_status(launch_gemm(a, stream));
+}
+
 TensorFuseStatus tensorfuse_b200_quantize_int8(const void* x, int dtype, long long n, signed char* q,
                                              float* scale_dev, cudaStream_t stream) {
   if (!x || !q || !scale_dev || n < 0) return TENSORFUSE_ERROR_INVALID_ARGUMENT;

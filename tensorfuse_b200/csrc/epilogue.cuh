@@ -27,6 +27,7 @@ struct EpiParams {
   float alpha, beta, scale;
   const float* scale_a;
   const float* scale_b;
+  const float* scale_cols = nullptr;   // optional: one dequantisation factor per output column (device, N floats)
 };
 
 __device__ __forceinline__ EpiParams resolve_scales(EpiParams ep) {

@@ -100,7 +100,9 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const TIn* __restrict__ 
     for (int i = 0; i < 8; ++i) {
       const int gm = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
       if (gm >= M) continue;
-      const float v = epilogue_value<EPI, kFp32Out>(acc[i][j], bv, ep);
+      EpiParams epn = ep;
+      if (EPI == kEpiI8Dequant && ep.scale_cols != nullptr) epn.scale = ep.scale * ep.scale_cols[gn];
+      const float v = epilogue_value<EPI, kFp32Out>(acc[i][j], bv, epn);
       if constexpr (EPI == kEpiI8Raw) C[(size_t)gm * N + gn] = (TOut)acc[i][j];
       else store_out(C + (size_t)gm * N + gn, v);
     }
@@ -111,7 +113,7 @@ template <typename TIn, typename TOut, int EPI>
 LaunchResult run(const GemmArgs& a, cudaStream_t stream) {
   dim3 grid((a.N + BN - 1) / BN, (a.M + BM - 1) / BM);
   if (grid.y > 65535u) return kUnsupported;
-  EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev};
+  EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev, a.scale_b_cols};
   gemm_simt_kernel<TIn, TOut, EPI><<<grid, 256, 0, stream>>>(
       static_cast<const TIn*>(a.A), static_cast<const TIn*>(a.B), a.bias, a.bias_dtype,
       static_cast<TOut*>(a.C), a.M, a.N, a.K, ep);

@@ -108,7 +108,7 @@ LaunchResult run(const GemmArgs& a, cudaStream_t stream) {
   const int tiles = ((a.M + TBM - 1) / TBM) * ((a.N + TBN - 1) / TBN);
   const int sms = sm_count(dev);
   const int grid = tiles < sms ? tiles : sms;
-  EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev};
+  EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev, a.scale_b_cols};
   kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, mc, a.bias, a.bias_dtype, a.M, a.N, a.K, ep,
                                                     watchdog_word());
   count_launch();
@@ -145,7 +145,7 @@ LaunchResult run_pair(const GemmArgs& a, cudaStream_t stream) {
   const int tiles = ((a.M + 2 * TBM - 1) / (2 * TBM)) * ((a.N + TBN - 1) / TBN);
   const int pairs_max = sm_count(dev) / 2;
   const int pairs = tiles < pairs_max ? tiles : pairs_max;
-  EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev};
+  EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev, a.scale_b_cols};
   kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(ma, mb, mc, a.bias, a.bias_dtype, a.M, a.N, a.K, ep,
                                                           watchdog_word());
   count_launch();
@@ -187,6 +187,7 @@ bool gemm_tc_eligible(const GemmArgs& a) {
   const int out_es = (a.out_dtype == kF16 || a.out_dtype == kBF16) ? 2 : 4;
   const uintptr_t ptrs = (uintptr_t)a.A | (uintptr_t)a.B | (uintptr_t)a.C;
   if (ptrs & 15u) return false;
+  if (a.scale_b_cols != nullptr && (((uintptr_t)a.scale_b_cols & 15u) || a.epilogue != kEpiI8Dequant)) return false;
   if (((size_t)a.K * es) % 16 || ((size_t)a.N * es) % 16 || ((size_t)a.N * out_es) % 16) return false;
   if (a.in_dtype == kF16) return a.out_dtype == kF16 && (a.epilogue == kEpiGelu || a.epilogue == kEpiLinear);
   if (a.in_dtype == kBF16) return a.out_dtype == kBF16 && (a.epilogue == kEpiGelu || a.epilogue == kEpiLinear);

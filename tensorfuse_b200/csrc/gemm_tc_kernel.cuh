@@ -199,6 +199,39 @@ __device__ __forceinline__ void epilogue_chunk(const uint32_t (&r)[32], const fl
   }
 }
 
+// Per-column dequantisation (weights quantised channel by channel): the factor of
+// column n is ep.scale * scale_cols[n], read through the read-only cache (the
+// same 32 values for every lane of the warp).  col0 is a multiple of 32 and N a
+// multiple of 16 on this path, so a float4 of factors is entirely inside or
+// outside the matrix.
+template <typename TOut, bool INT_ACC>
+__device__ __forceinline__ void epilogue_chunk_cols(const uint32_t (&r)[32], const float* bs, const EpiParams& ep,
+                                                    int col0, int N, uint32_t (&w)[32]) {
+  constexpr bool kFp32Out = sizeof(TOut) == 4;
+#pragma unroll
+  for (int i = 0; i < 32; i += 4) {
+    const float4 b4 = *reinterpret_cast<const float4*>(bs + i);
+    float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (col0 + i < N) s4 = __ldg(reinterpret_cast<const float4*>(ep.scale_cols + col0 + i));
+    const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, ss[4] = {s4.x, s4.y, s4.z, s4.w};
+    float v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float a = INT_ACC ? (float)(int)r[i + u] : __uint_as_float(r[i + u]);
+      const float x = fmaf(a, ep.scale * ss[u], bb[u]);
+      v[u] = kFp32Out ? gelu_accurate(x) : gelu_fast(x);
+    }
+    if constexpr (sizeof(TOut) == 2) {
+      const __half2 h0 = __floats2half2_rn(v[0], v[1]), h1 = __floats2half2_rn(v[2], v[3]);
+      w[i / 2] = *reinterpret_cast<const uint32_t*>(&h0);
+      w[i / 2 + 1] = *reinterpret_cast<const uint32_t*>(&h1);
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) w[i + u] = __float_as_uint(v[u]);
+    }
+  }
+}
+
 // The epilogue of one 128 x 256 accumulator, shared by the single-CTA and the
 // CTA-pair kernel: stage the bias slice, wait for the accumulator, then per 32
 // columns TMEM -> registers -> scale/bias/activation -> staging box -> TMA
@@ -247,7 +280,10 @@ __device__ __forceinline__ bool epilogue_tile(const CUtensorMap* tmC, const void
       release();
     }
     uint32_t w[32];
-    epilogue_chunk<EPI, TOut, INT_ACC>(acc[c & 1], bsh + c * 32, ep, w);
+    if (EPI == kEpiI8Dequant && ep.scale_cols != nullptr)
+      epilogue_chunk_cols<TOut, INT_ACC>(acc[c & 1], bsh + c * 32, ep, nc + c * 32, N, w);
+    else
+      epilogue_chunk<EPI, TOut, INT_ACC>(acc[c & 1], bsh + c * 32, ep, w);
     if (c % CHUNKS_PER_BOX == 0) {
       if (lane == 0) bulk_wait_read_all();   // the previous box has left the staging buffer
       __syncwarp();

@@ -66,6 +66,8 @@ struct GemmArgs {
   float alpha, beta, scale;       // scale: product of the host-known dequant factors
   const float* scale_a_dev;       // optional device pointers to one float each; multiplied
   const float* scale_b_dev;       // into `scale` on the device
+  const float* scale_b_cols;      // optional device array of N floats: per-column factor of B (kEpiI8Dequant only);
+                                  // needs 16-byte alignment
 };
 
 // True when the tensor-core (TMA + tcgen05) kernel can take this problem:
@@ -113,6 +115,12 @@ LaunchResult launch_quantize_int8(const void* x, int dtype, long long n, signed 
 // (residual may be null); FP32 arithmetic, x/residual/gamma/beta/out of `dtype`.
 LaunchResult launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
                                   long long rows, int hidden, int dtype, float eps, cudaStream_t stream);
+
+// Column-wise variant for weights: scales[n] = max_k |w[k,n]| / 127 (1 for an
+// all-zero column), q[k,n] = clip(rint(w[k,n] / scales[n]), -127, 127); w is
+// [K, N] row-major FP16 or FP32.
+LaunchResult launch_quantize_int8_columns(const void* w, int dtype, int K, int N, signed char* q, float* scales_dev,
+                                          cudaStream_t stream);
 
 // Device-side watchdog: 0 when no bounded wait has expired since the last
 // reset, else the code of the first wait that gave up.

@@ -122,6 +122,53 @@ __global__ void __launch_bounds__(256) quantize_kernel(const T* __restrict__ x, 
   for (long long i = n8 * 8 + tid; i < n; i += nthreads) q[i] = (int8_t)quant1(widen<T>(x[i]), s);
 }
 
+// Column-wise: one thread per column walks the K rows (neighbouring threads read
+// neighbouring columns, so every row segment is one coalesced access); rows are
+// split over blockIdx.y and merged with an atomic maximum on the bit patterns.
+template <typename T>
+__global__ void __launch_bounds__(256) absmax_columns_kernel(const T* __restrict__ w, int K, int N, unsigned* out) {
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  if (n >= N) return;
+  const int rows_per = (K + gridDim.y - 1) / gridDim.y;
+  const int k0 = blockIdx.y * rows_per, k1 = min(K, k0 + rows_per);
+  float m = 0.0f;
+  for (int k = k0; k < k1; ++k) m = fmaxf(m, fabsf(widen<T>(w[(size_t)k * N + n])));
+  atomicMax(out + n, __float_as_uint(m));
+}
+__global__ void __launch_bounds__(256) scales_from_absmax_kernel(float* words, int N) {
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  if (n >= N) return;
+  const float amax = words[n];
+  words[n] = amax > 0.0f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+}
+template <typename T>
+__global__ void __launch_bounds__(256) quantize_columns_kernel(const T* __restrict__ w, int K, int N,
+                                                               const float* __restrict__ scales,
+                                                               int8_t* __restrict__ q) {
+  const int n = blockIdx.x * 256 + threadIdx.x;
+  if (n >= N) return;
+  const float s = scales[n];
+  const int rows_per = (K + gridDim.y - 1) / gridDim.y;
+  const int k0 = blockIdx.y * rows_per, k1 = min(K, k0 + rows_per);
+  for (int k = k0; k < k1; ++k) q[(size_t)k * N + n] = (int8_t)quant1(widen<T>(w[(size_t)k * N + n]), s);
+}
+
+template <typename T>
+LaunchResult run_columns(const void* w, int K, int N, int8_t* q, float* scales, cudaStream_t stream) {
+  const unsigned gx = (unsigned)((N + 255) / 256);
+  unsigned gy = (unsigned)((8 * 148 + gx - 1) / gx);       // enough CTAs to fill the device
+  if (gy > (unsigned)K) gy = (unsigned)K;
+  if (gy < 1) gy = 1;
+  if (gy > 65535u) gy = 65535u;
+  if (cudaMemsetAsync(scales, 0, sizeof(float) * (size_t)N, stream) != cudaSuccess) return kCudaError;
+  absmax_columns_kernel<T><<<dim3(gx, gy), 256, 0, stream>>>(static_cast<const T*>(w), K, N,
+                                                            reinterpret_cast<unsigned*>(scales));
+  scales_from_absmax_kernel<<<gx, 256, 0, stream>>>(scales, N);
+  quantize_columns_kernel<T><<<dim3(gx, gy), 256, 0, stream>>>(static_cast<const T*>(w), K, N, scales, q);
+  count_launch(3);
+  return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
+}
+
 int sm_count_now() {
   int dev = 0, n = 0;
   cudaGetDevice(&dev);
@@ -154,6 +201,15 @@ LaunchResult launch_quantize_int8(const void* x, int dtype, long long n, signed 
   if (n == 0) return kOk;
   if (dtype == kF16) return run<__half>(x, n, reinterpret_cast<int8_t*>(q), scale_dev, stream);
   return run<float>(x, n, reinterpret_cast<int8_t*>(q), scale_dev, stream);
+}
+
+LaunchResult launch_quantize_int8_columns(const void* w, int dtype, int K, int N, signed char* q, float* scales_dev,
+                                          cudaStream_t stream) {
+  if (!w || !q || !scales_dev || K < 0 || N < 0) return kInvalidArgument;
+  if (dtype != kF16 && dtype != kF32) return kUnsupported;
+  if (K == 0 || N == 0) return kOk;
+  if (dtype == kF16) return run_columns<__half>(w, K, N, reinterpret_cast<int8_t*>(q), scales_dev, stream);
+  return run_columns<float>(w, K, N, reinterpret_cast<int8_t*>(q), scales_dev, stream);
 }
 
 }  // namespace tfb

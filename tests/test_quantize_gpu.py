@@ -56,3 +56,33 @@ def test_quantize_then_int8_gemm_stays_on_device(tf, oracle):
     acc = oracle.gemm_i8_acc(oa, ow)
     want = oracle.i8_epilogue_f16(acc, b, float(osa), float(osw))
     assert oracle.f16_parity_violations(host(out), want, max_ulp=1) == 0
+
+
+@pytest.mark.parametrize("K,N,dtype", [(512, 384, np.float32), (1000, 72, np.float16), (64, 4096, np.float32)])
+def test_quantize_columns_matches_oracle(tf, oracle, K, N, dtype):
+    rng = np.random.default_rng(12)
+    w = (rng.standard_normal((K, N)) * rng.uniform(0.01, 3.0, N)[None, :]).astype(dtype)
+    w[:, 5] = 0                                     # an all-zero channel
+    q, s = tf.quantize_int8(dev(w), per_column=True)
+    wq, ws = oracle.quantize_sym_int8_columns(w)
+    assert np.array_equal(host(s), ws)
+    assert np.array_equal(host(q), wq)
+
+
+@pytest.mark.parametrize("M,K,N", [(512, 512, 384), (100, 96, 80), (37, 50, 21)])
+def test_channelwise_int8_gemm(tf, oracle, M, K, N):
+    """Per-tensor activation scale x per-column weight scales, everything on the
+    device; FP16 result within 1 ulp of the float64 formula on the exact accumulators."""
+    import tensorfuse_b200 as t
+    rng = np.random.default_rng(3)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    W = (rng.standard_normal((K, N)) * rng.uniform(0.02, 1.0, N)[None, :] / np.sqrt(K)).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.02).astype(np.float16)
+    qa, sa = tf.quantize_int8(dev(A)); qw, sw = tf.quantize_int8(dev(W), per_column=True)
+    out = tf.fused_gemm_bias_gelu(qa, qw, dev(b), scales=(sa, sw), out_dtype=torch.float16, int8_mode=t.INT8_DEQUANT)
+    check_watchdog()
+    oa, osa = oracle.quantize_sym_int8(A); ow, osw = oracle.quantize_sym_int8_columns(W)
+    acc = oracle.gemm_i8_acc(oa, ow).astype(np.float64)
+    x = acc * (np.float64(osa) * osw.astype(np.float64))[None, :] + b.astype(np.float64)
+    ref = (0.5 * x * (1.0 + np.tanh(0.7978845608028654 * (x + 0.044715 * x ** 3)))).astype(np.float16)
+    assert oracle.f16_parity_violations(host(out), ref, max_ulp=1) == 0
