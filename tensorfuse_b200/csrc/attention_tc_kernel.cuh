@@ -334,14 +334,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float ls0 = 0.0f, ls1 = 0.0f;
       const float nm = -m_new;
       tmem_ld_32x32(tS, r[0]);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld_wait();
-        if (c < 3) tmem_ld_32x32(tS + (c + 1) * 32, r[(c + 1) & 1]);
-        else {
-          tc_fence_before();
-          mbar_arrive(bar_s_free);            // S may be overwritten by the next block's scores
-        }
+      // Two chunks per trip (the two register buffers alternate), the trip itself not
+      // unrolled: half the code of a fully unrolled sweep, which matters for the
+      // instruction cache with two CTAs' warps at different places of this kernel.
+      auto chunk = [&](int c, const uint32_t (&rc)[32]) {
         // dropout decisions of the 32 keys of this chunk: four Philox blocks at once
         uint32_t km[4][4];
         if (DROP) {
@@ -368,11 +364,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           const int i = 2 * k;
           float e0, e1;
           if (!DROP && (k & 3) == 3) {
-            e0 = exp2_poly3(fmaf(__uint_as_float(r[c & 1][i]), sl2, nm));
-            e1 = exp2_poly3(fmaf(__uint_as_float(r[c & 1][i + 1]), sl2, nm));
+            e0 = exp2_poly3(fmaf(__uint_as_float(rc[i]), sl2, nm));
+            e1 = exp2_poly3(fmaf(__uint_as_float(rc[i + 1]), sl2, nm));
           } else {
-            e0 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i]), sl2, nm));
-            e1 = ex2_approx(fmaf(__uint_as_float(r[c & 1][i + 1]), sl2, nm));
+            e0 = ex2_approx(fmaf(__uint_as_float(rc[i]), sl2, nm));
+            e1 = ex2_approx(fmaf(__uint_as_float(rc[i + 1]), sl2, nm));
           }
           if (TAIL) {
             if (c * 32 + i >= valid) e0 = 0.0f;
@@ -384,6 +380,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (DROP) w[k] &= km[k >> 2][k & 3];
         }
         tmem_st_32x16(tP + c * 16, w);
+      };
+#pragma unroll 1
+      for (int cc = 0; cc < 2; ++cc) {
+        tmem_ld_wait();
+        tmem_ld_32x32(tS + (2 * cc + 1) * 32, r[1]);
+        chunk(2 * cc, r[0]);
+        tmem_ld_wait();
+        if (cc == 0) tmem_ld_32x32(tS + 64, r[0]);
+        else {
+          tc_fence_before();
+          mbar_arrive(bar_s_free);            // S may be overwritten by the next block's scores
+        }
+        chunk(2 * cc + 1, r[1]);
       }
       tmem_st_wait();
       return ls0 + ls1;
