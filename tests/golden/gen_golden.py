@@ -1,8 +1,9 @@
 #!/usr/bin/env python3
 """Generate tests/golden/reference_numpy_oracle.npz.
 
-Run in a container that has the reference project checked out (default
-location /root/reference, override with TENSORFUSE_REFERENCE).  The script
+Run where the reference project is checked out:
+    python tests/golden/gen_golden.py <path of the reference checkout>
+(or set TENSORFUSE_REFERENCE).  The script
 imports the reference's OWN numpy oracle functions from
 ``src/tests/python/test_mathematical_verification.py`` (gelu_reference,
 gemm_bias_gelu_reference, softmax_reference) and the quantisation recipe of
@@ -17,7 +18,9 @@ import sys
 
 import numpy as np
 
-REF = os.environ.get("TENSORFUSE_REFERENCE", "/root/reference")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TENSORFUSE_REFERENCE", "")
+if not REF or not os.path.isdir(REF):
+    sys.exit(__doc__)
 SRC = os.path.join(REF, "src/tests/python/test_mathematical_verification.py")
 
 
