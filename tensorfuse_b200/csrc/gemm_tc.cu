@@ -143,7 +143,22 @@ LaunchResult run_pair(const GemmArgs& a, cudaStream_t stream) {
       !cached_map(MapKey{a.C, (int)sizeof(TOut), a.M, a.N, 32}, &mc))
     return kLaunchFailed;
   const int tiles = ((a.M + 2 * TBM - 1) / (2 * TBM)) * ((a.N + TBN - 1) / TBN);
-  const int pairs_max = sm_count(dev) / 2;
+  // one resident cluster per SM pair the device can actually co-schedule
+  static int max_clusters[64] = {};
+  if (max_clusters[dev] == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)(sm_count(dev) / 2));
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = sm_count(dev) / 2; }
+    max_clusters[dev] = n;
+  }
+  const int pairs_max = max_clusters[dev];
   const int pairs = tiles < pairs_max ? tiles : pairs_max;
   EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev, a.scale_b_cols};
   kernel<<<2 * pairs, NUM_THREADS, P_SMEM_BYTES, stream>>>(ma, mb, mc, a.bias, a.bias_dtype, a.M, a.N, a.K, ep,
