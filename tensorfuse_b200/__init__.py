@@ -543,7 +543,7 @@ def fused_multi_head_attention(query, key, value, output=None, num_heads=1, drop
     if k.dtype != q.dtype or v.dtype != q.dtype:
         raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(Status.INVALID_ARGUMENT))
     dt = _torch_dt(q)
-    if dt not in (DataType.FLOAT16, DataType.FLOAT32):
+    if dt not in (DataType.FLOAT16, DataType.BFLOAT16, DataType.FLOAT32):
         raise RuntimeError("fused_multi_head_attention failed: " + get_error_string(Status.UNSUPPORTED_OPERATION))
     lens_ptr = None
     if kv_lengths is not None:

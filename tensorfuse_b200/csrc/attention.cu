@@ -7,6 +7,7 @@
 // query/key/value/output are [batch, seq_len, hidden_dim], dropout acts on the
 // attention weights).  Here it computes.
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
 
@@ -35,9 +36,11 @@ struct SimtParams {
 template <typename T> __device__ __forceinline__ float to_f(T x);
 template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
 template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
 template <typename T> __device__ __forceinline__ T from_f(float x);
 template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
 template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 
 constexpr int kSimtWarps = 4;
 constexpr int kMaxHd = 256;
@@ -122,6 +125,7 @@ LaunchResult run_simt(const AttnArgs& a, float scale, cudaStream_t stream) {
   const long long blocks = (rows + kSimtWarps - 1) / kSimtWarps;
   if (blocks > 0x7FFFFFFFll) return kUnsupported;
   if (a.dtype == kF16) attention_simt_kernel<__half><<<(unsigned)blocks, kSimtWarps * 32, 0, stream>>>(sp);
+  else if (a.dtype == kBF16) attention_simt_kernel<__nv_bfloat16><<<(unsigned)blocks, kSimtWarps * 32, 0, stream>>>(sp);
   else attention_simt_kernel<float><<<(unsigned)blocks, kSimtWarps * 32, 0, stream>>>(sp);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? kOk : kLaunchFailed;
@@ -165,10 +169,10 @@ bool cached_map4(const Map4Key& k, CUtensorMap* out) {
   return true;
 }
 
-template <bool DROP>
+template <bool DROP, bool BF16>
 LaunchResult run_tc(const AttnArgs& a, float scale, cudaStream_t stream) {
   using namespace attn;
-  auto kernel = attention_tc_kernel<DROP>;
+  auto kernel = attention_tc_kernel<DROP, BF16>;
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) return kCudaError;
@@ -215,7 +219,7 @@ LaunchResult run_tc(const AttnArgs& a, float scale, cudaStream_t stream) {
 }  // namespace
 
 bool attention_tc_eligible(const AttnArgs& a) {
-  if (a.dtype != kF16 || a.head_dim != attn::HD) return false;
+  if ((a.dtype != kF16 && a.dtype != kBF16) || a.head_dim != attn::HD) return false;
   const uintptr_t ptrs = (uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out;
   if (ptrs & 15u) return false;
   const long long strides[12] = {a.ld_q, a.ld_k, a.ld_v, a.ld_o, a.hs_q, a.hs_k, a.hs_v, a.hs_o,
@@ -228,13 +232,16 @@ bool attention_tc_eligible(const AttnArgs& a) {
 
 LaunchResult launch_attention(const AttnArgs& a, cudaStream_t stream) {
   if (!a.q || !a.k || !a.v || !a.out) return kInvalidArgument;
-  if (a.dtype != kF16 && a.dtype != kF32) return kUnsupported;
+  if (a.dtype != kF16 && a.dtype != kBF16 && a.dtype != kF32) return kUnsupported;
   if (a.batch < 0 || a.seq_q < 0 || a.seq_kv < 0 || a.heads <= 0 || a.head_dim <= 0) return kInvalidArgument;
   if (!(a.p >= 0.0f && a.p <= 1.0f)) return kInvalidArgument;
   if (a.batch == 0 || a.seq_q == 0) return kOk;
   const float scale = a.scale > 0.0f ? a.scale : 1.0f / sqrtf((float)a.head_dim);
-  if (a.seq_kv > 0 && attention_tc_eligible(a))
-    return dropout_threshold(a.p) != 0u ? run_tc<true>(a, scale, stream) : run_tc<false>(a, scale, stream);
+  if (a.seq_kv > 0 && attention_tc_eligible(a)) {
+    const bool drop = dropout_threshold(a.p) != 0u;
+    if (a.dtype == kBF16) return drop ? run_tc<true, true>(a, scale, stream) : run_tc<false, true>(a, scale, stream);
+    return drop ? run_tc<true, false>(a, scale, stream) : run_tc<false, false>(a, scale, stream);
+  }
   return run_simt(a, scale, stream);
 }
 

@@ -37,6 +37,7 @@
 // tear-down that frees TMEM.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include "kernels.h"
@@ -109,7 +110,21 @@ __device__ __forceinline__ float exp2_poly3(float t) {
   return __int_as_float(__float_as_int(q) + (__float_as_int(y) << 23));
 }
 
-template <bool DROP>
+// Two FP32 values -> one word of two 16-bit values of the tensor's type.
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+  if constexpr (BF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  } else {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+}
+
+// BF16 = false: FP16 tensors; true: BF16 tensors (same layouts, the MMAs take the
+// other 16-bit format, probabilities and output are rounded to BF16).
+template <bool DROP, bool BF16>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
@@ -202,8 +217,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (elect_one()) {
-      constexpr uint32_t IDESC_S = make_idesc_major(1u, 0u, 0u, 0u, BQ, BKV);   // Q, K: K-major
-      constexpr uint32_t IDESC_O = make_idesc_major(1u, 0u, 0u, 1u, BQ, HD);    // P K-major, V MN-major
+      constexpr uint32_t FMT = BF16 ? 1u : 0u;
+      constexpr uint32_t IDESC_S = make_idesc_major(1u, FMT, 0u, 0u, BQ, BKV);   // Q, K: K-major
+      constexpr uint32_t IDESC_O = make_idesc_major(1u, FMT, 0u, 1u, BQ, HD);    // P K-major, V MN-major
       const uint32_t tS = tmem_base, tO = tmem_base + 128, tP = tmem_base + 192;
       // S = Q K^T of key block number gi (counted over the whole CTA)
       auto issue_s = [&](uint32_t gi, bool last_of_item) -> bool {
@@ -375,8 +391,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (c * 32 + i + 1 >= valid) e1 = 0.0f;
           }
           ls0 += e0; ls1 += e1;
-          const __half2 hh = __floats2half2_rn(e0, e1);
-          w[k] = *reinterpret_cast<const uint32_t*>(&hh);
+          w[k] = pack16<BF16>(e0, e1);
           if (DROP) w[k] &= km[k >> 2][k & 3];
         }
         tmem_st_32x16(tP + c * 16, w);
@@ -453,8 +468,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int i = gq * 8 + 2 * k;
-            const __half2 hh = __floats2half2_rn(__uint_as_float(r[0][i]) * inv, __uint_as_float(r[0][i + 1]) * inv);
-            w[k] = *reinterpret_cast<const uint32_t*>(&hh);
+            w[k] = pack16<BF16>(__uint_as_float(r[0][i]) * inv, __uint_as_float(r[0][i + 1]) * inv);
           }
           const uint32_t addr = sP + row * 128 + (((c * 4 + gq) ^ (row & 7)) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])

@@ -340,7 +340,7 @@ TensorFuseStatus tensorfuse_fused_multi_head_attention(const TensorFuseTensor* q
     return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
   if (query->dtype != key->dtype || query->dtype != value->dtype || query->dtype != output->dtype)
     return TENSORFUSE_ERROR_INVALID_ARGUMENT;
-  if (query->dtype != TENSORFUSE_FLOAT16 && query->dtype != TENSORFUSE_FLOAT32)
+  if (query->dtype != TENSORFUSE_FLOAT16 && query->dtype != TENSORFUSE_BFLOAT16 && query->dtype != TENSORFUSE_FLOAT32)
     return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
   if (B == 0 || Sq == 0 || H == 0) return TENSORFUSE_SUCCESS;
   if (!query->data || !key->data || !value->data || !output->data) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
@@ -348,7 +348,8 @@ TensorFuseStatus tensorfuse_fused_multi_head_attention(const TensorFuseTensor* q
   t_last_seed = seed;
   return tensorfuse_b200_attention(query->data, key->data, value->data, output->data, B, Sq, Skv, num_heads,
                                    H / num_heads, H, H, H, H, 0, 0, 0, 0, 0, 0, 0, 0,
-                                   query->dtype == TENSORFUSE_FLOAT16 ? kF16 : kF32, 0.0f, dropout_prob, seed,
+                                   query->dtype == TENSORFUSE_FLOAT16 ? kF16 : query->dtype == TENSORFUSE_BFLOAT16 ? kBF16 : kF32,
+                                   0.0f, dropout_prob, seed,
                                    nullptr, stream);
 }
 

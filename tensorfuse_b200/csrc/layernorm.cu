@@ -9,6 +9,7 @@
 // not E[x^2] - mean^2) and the normalisation.  Rows up to 2048 elements with
 // 16-byte aligned pitches take this path; anything else takes a block-per-row
 // kernel that re-reads the row.
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
 
@@ -38,6 +39,26 @@ template <> struct Io8<__half> {
     *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 };
+template <> struct Io8<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&x)[8]) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {          // a BF16 value is the upper half of the FP32 with the same value
+      x[2 * k] = __uint_as_float(w[k] << 16);
+      x[2 * k + 1] = __uint_as_float(w[k] & 0xFFFF0000u);
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&x)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * k], x[2 * k + 1]);
+      w[k] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
 template <> struct Io8<float> {
   static __device__ __forceinline__ void load(const float* p, float (&x)[8]) {
     const float4 a = *reinterpret_cast<const float4*>(p), b = *(reinterpret_cast<const float4*>(p) + 1);
@@ -51,9 +72,11 @@ template <> struct Io8<float> {
 template <typename T> __device__ __forceinline__ float ld1(const T* p);
 template <> __device__ __forceinline__ float ld1<float>(const float* p) { return *p; }
 template <> __device__ __forceinline__ float ld1<__half>(const __half* p) { return __half2float(*p); }
+template <> __device__ __forceinline__ float ld1<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
 template <typename T> __device__ __forceinline__ void st1(T* p, float v);
 template <> __device__ __forceinline__ void st1<float>(float* p, float v) { *p = v; }
 template <> __device__ __forceinline__ void st1<__half>(__half* p, float v) { *p = __float2half_rn(v); }
+template <> __device__ __forceinline__ void st1<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -184,9 +207,10 @@ LaunchResult run(const void* x, const void* res, const void* gamma, const void* 
 LaunchResult launch_add_layernorm(const void* x, const void* residual, const void* gamma, const void* beta, void* out,
                                   long long rows, int hidden, int dtype, float eps, cudaStream_t stream) {
   if (!x || !gamma || !beta || !out || rows < 0 || hidden <= 0) return kInvalidArgument;
-  if (dtype != kF16 && dtype != kF32) return kUnsupported;
+  if (dtype != kF16 && dtype != kBF16 && dtype != kF32) return kUnsupported;
   if (rows == 0) return kOk;
   if (dtype == kF16) return run<__half>(x, residual, gamma, beta, out, rows, hidden, eps, stream);
+  if (dtype == kBF16) return run<__nv_bfloat16>(x, residual, gamma, beta, out, rows, hidden, eps, stream);
   return run<float>(x, residual, gamma, beta, out, rows, hidden, eps, stream);
 }
 

@@ -75,7 +75,8 @@ extern "C" TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseT
     if (output->shape.dims[i] != input->shape.dims[i]) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
   const TensorFuseDataType dt = input->dtype;
   if (output->dtype != dt) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
-  if (dt != TENSORFUSE_FLOAT16 && dt != TENSORFUSE_FLOAT32) return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
+  if (dt != TENSORFUSE_FLOAT16 && dt != TENSORFUSE_BFLOAT16 && dt != TENSORFUSE_FLOAT32)
+    return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
   int epi_ffn;
   if (p->ffn_activation == TENSORFUSE_ACTIVATION_GELU) epi_ffn = kEpiGelu;
   else if (p->ffn_activation == TENSORFUSE_ACTIVATION_NONE) epi_ffn = kEpiLinear;
@@ -98,8 +99,8 @@ extern "C" TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseT
   if (!input->data || !output->data) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
   if (tokens > 0x7FFFFFFFll) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
   const int M = (int)tokens;
-  const int kdt = dt == TENSORFUSE_FLOAT16 ? kF16 : kF32;
-  const size_t es = kdt == kF16 ? 2 : 4;
+  const int kdt = dt == TENSORFUSE_FLOAT16 ? kF16 : dt == TENSORFUSE_BFLOAT16 ? kBF16 : kF32;
+  const size_t es = kdt == kF32 ? 4 : 2;
 
   const int dev = device_of_pointer(output->data);
   DeviceGuard guard(dev);
