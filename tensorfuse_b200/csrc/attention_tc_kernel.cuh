@@ -347,8 +347,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     // dropout, FP16 tile P (K-major, 128-byte swizzle).  Returns the row sum.
     auto pass2 = [&](auto tail_c, int valid, int j, float m_new) -> float {
       constexpr bool TAIL = decltype(tail_c)::value;
-      float ls0 = 0.0f, ls1 = 0.0f;
-      const float nm = -m_new;
+      uint64_t ls2 = pack2(0.0f, 0.0f);
+      const uint64_t sl2_2 = pack2(sl2, sl2), nm_2 = pack2(-m_new, -m_new);
       tmem_ld_32x32(tS, r[0]);
       // Two chunks per trip (the two register buffers alternate), the trip itself not
       // unrolled: half the code of a fully unrolled sweep, which matters for the
@@ -378,19 +378,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int k = 0; k < 16; ++k) {
           const int i = 2 * k;
+          // one packed FMA for the pair (the two scores sit in an aligned register pair)
+          const float2 t = unpack2(fma2(pack2(__uint_as_float(rc[i]), __uint_as_float(rc[i + 1])), sl2_2, nm_2));
           float e0, e1;
-          if (!DROP && (k & 3) == 3) {
-            e0 = exp2_poly3(fmaf(__uint_as_float(rc[i]), sl2, nm));
-            e1 = exp2_poly3(fmaf(__uint_as_float(rc[i + 1]), sl2, nm));
-          } else {
-            e0 = ex2_approx(fmaf(__uint_as_float(rc[i]), sl2, nm));
-            e1 = ex2_approx(fmaf(__uint_as_float(rc[i + 1]), sl2, nm));
-          }
+          if (!DROP && (k & 3) == 3) { e0 = exp2_poly3(t.x); e1 = exp2_poly3(t.y); }
+          else { e0 = ex2_approx(t.x); e1 = ex2_approx(t.y); }
           if (TAIL) {
             if (c * 32 + i >= valid) e0 = 0.0f;
             if (c * 32 + i + 1 >= valid) e1 = 0.0f;
           }
-          ls0 += e0; ls1 += e1;
+          ls2 = add2(ls2, pack2(e0, e1));
           w[k] = pack16<BF16>(e0, e1);
           if (DROP) w[k] &= km[k >> 2][k & 3];
         }
@@ -410,7 +407,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         chunk(2 * cc + 1, r[1]);
       }
       tmem_st_wait();
-      return ls0 + ls1;
+      const float2 ls = unpack2(ls2);
+      return ls.x + ls.y;
     };
 
     for (int t = blockIdx.x; t < p.n_tiles && ok; t += gridDim.x) {
