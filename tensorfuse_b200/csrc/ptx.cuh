@@ -43,14 +43,21 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// One poll: the hardware may park the thread for up to kTryWaitSuspendNs before
+// it answers, and wakes it as soon as the phase completes, so a waiting warp
+// does not eat the issue slots of the warps it is waiting for.
+#ifndef TFB_TRY_WAIT_SUSPEND_NS
+#define TFB_TRY_WAIT_SUSPEND_NS 20000
+#endif
+constexpr uint32_t kTryWaitSuspendNs = TFB_TRY_WAIT_SUSPEND_NS;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kTryWaitSuspendNs)
       : "memory");
   return ok != 0;
 }
