@@ -100,6 +100,32 @@ class ClockSampler:
                 "samples": len(mhz)}
 
 
+# ------------------------------------------------------------ host placement
+def bind_near_gpu(local: int):
+    """Restricts this process to the CPUs of the NUMA node its GPU hangs off, so that
+    the pinned host buffers of the end-to-end leg are allocated there and every
+    rank's copies stay on its own socket and PCIe root.  Returns the node or None."""
+    try:
+        out = subprocess.run(["nvidia-smi", "--query-gpu=pci.bus_id", "--format=csv,noheader", "-i", str(local)],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        dom, rest = out.split(":", 1)
+        bdf = f"{int(dom, 16):04x}:{rest}"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except Exception:
+        return None
+
+
 # --------------------------------------------------------------- reference arm
 _CPU_OPS = None
 
@@ -264,6 +290,7 @@ def run_gpu(args):
         clocks["window"] = f"{n_sus} back-to-back steps ({t_sus1 - t_sus0:.2f} s) run right after the timed steps"
 
     # ---- end to end: host operands (pinned), copies inside the timed region
+    numa_node = bind_near_gpu(local) if world > 1 else None
     pA = tf.pinned_empty((M, K), np.float16); pA[...] = A_h
     pB = tf.pinned_empty((K, N), np.float16); pB[...] = B_h
     pb = tf.pinned_empty((N,), np.float16); pb[...] = b_h
@@ -316,7 +343,8 @@ def run_gpu(args):
                      if peaks.get("tflops_sustained") else None},
         "cpu_baseline": cpu,
         "e2e": {"value": e2e_val, "unit": "TFLOPS", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_s * 1e3, "api": "tensorfuse_b200.fused_gemm_bias_gelu(numpy) -> "
+                "ms_per_step": e2e_s * 1e3, "host_numa_node_rank0": numa_node,
+                "api": "tensorfuse_b200.fused_gemm_bias_gelu(numpy) -> "
                                                    "tensorfuse_b200_gemm_bias_gelu_host"},
         "gpu_launches": int(launches),
         "clocks": clocks,
