@@ -72,6 +72,31 @@ __device__ __forceinline__ void philox_block_x4(unsigned long long blk, const ui
 #pragma unroll
   for (int q = 0; q < 4; ++q) { o[q][0] = a0[q]; o[q][1] = a1[q]; o[q][2] = a2[q]; o[q][3] = a3[q]; }
 }
+// NB independent blocks (arbitrary counters), rounds outermost so that the
+// dependency chains interleave.
+template <int NB>
+__device__ __forceinline__ void philox_blocks(const unsigned long long (&blk)[NB], const uint32_t* key,
+                                              uint32_t (&o)[NB][4]) {
+  uint32_t a0[NB], a1[NB], a2[NB], a3[NB];
+#pragma unroll
+  for (int q = 0; q < NB; ++q) { a0[q] = (uint32_t)blk[q]; a1[q] = (uint32_t)(blk[q] >> 32); a2[q] = 0u; a3[q] = 0u; }
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+#pragma unroll
+    for (int q = 0; q < NB; ++q) {
+      const uint64_t p0 = (uint64_t)0xD2511F53u * a0[q];
+      const uint64_t p1 = (uint64_t)0xCD9E8D57u * a2[q];
+      const uint32_t n0 = (uint32_t)(p1 >> 32) ^ a1[q] ^ key[2 * r];
+      const uint32_t n2 = (uint32_t)(p0 >> 32) ^ a3[q] ^ key[2 * r + 1];
+      a1[q] = (uint32_t)p1;
+      a3[q] = (uint32_t)p0;
+      a0[q] = n0;
+      a2[q] = n2;
+    }
+  }
+#pragma unroll
+  for (int q = 0; q < NB; ++q) { o[q][0] = a0[q]; o[q][1] = a1[q]; o[q][2] = a2[q]; o[q][3] = a3[q]; }
+}
 // Keep decision of the single element `idx` (global element index).
 __device__ __forceinline__ bool philox_keep(unsigned long long idx, const uint32_t* key, uint32_t thr) {
   uint32_t o[4];

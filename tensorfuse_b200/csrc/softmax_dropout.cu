@@ -204,6 +204,27 @@ template <> struct Unit<float> {
 // order exactly like non-negative FP16 numbers (patterns above 0x7C00 are NaNs,
 // for which "greater-or-unordered" is true, as it must be), so one packed FP16
 // compare decides two elements.
+// Raw Philox words of one block -> the four mask words.
+template <bool DROP>
+__device__ __forceinline__ void masks_from_words(const SmParams& p, const uint32_t (&o)[4], uint32_t (&km)[4]) {
+  if (DROP) {
+    if (p.hcmp) {
+      const __half2 thr2 = *reinterpret_cast<const __half2*>(&p.thr_h2);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t f = o[k] & 0x7FFF7FFFu;
+        km[k] = __hgeu2_mask(*reinterpret_cast<const __half2*>(&f), thr2);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        km[k] = ((o[k] & 0x7FFFu) >= p.thr ? 0x0000FFFFu : 0u) | (((o[k] >> 16) & 0x7FFFu) >= p.thr ? 0xFFFF0000u : 0u);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) km[k] = 0xFFFFFFFFu;
+  }
+}
 template <bool DROP>
 __device__ __forceinline__ void keep_masks(const SmParams& p, unsigned long long philox_blk, uint32_t (&km)[4]) {
   if (DROP) {
@@ -229,11 +250,19 @@ __device__ __forceinline__ void keep_masks(const SmParams& p, unsigned long long
 
 // Scale, drop and store one unit.  e2[k] holds elements 2k, 2k+1.
 template <typename T, bool DROP>
+__device__ __forceinline__ void finish_unit_masked(const uint64_t (&e2)[4], uint64_t g2, T* out, unsigned char* mask,
+                                                   const uint32_t (&km)[4]);
+template <typename T, bool DROP>
 __device__ __forceinline__ void finish_unit(const uint64_t (&e2)[4], uint64_t g2, T* out,
                                             unsigned char* mask, const SmParams& p,
                                             unsigned long long philox_blk) {
   uint32_t km[4];
   keep_masks<DROP>(p, philox_blk, km);
+  finish_unit_masked<T, DROP>(e2, g2, out, mask, km);
+}
+template <typename T, bool DROP>
+__device__ __forceinline__ void finish_unit_masked(const uint64_t (&e2)[4], uint64_t g2, T* out, unsigned char* mask,
+                                                   const uint32_t (&km)[4]) {
   uint2 mb;   // one byte per element: byte 0 / 2 of each mask word, reduced to 0 / 1
   mb.x = __byte_perm(km[0], km[1], 0x6420) & 0x01010101u;
   mb.y = __byte_perm(km[2], km[3], 0x6420) & 0x01010101u;
@@ -303,6 +332,29 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
       else nxt[c].fill_neg_inf();
     }
 
+    // Dropout decisions of this lane's units.  They depend on positions only, so they are
+    // generated here, up to four Philox blocks with interleaved rounds, where their integer
+    // work overlaps the latency of the loads above and the reductions below.
+    uint32_t km[CH][4];
+    {
+      const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)L) >> 3;
+      constexpr int NB = CH < 4 ? CH : 4;
+#pragma unroll
+      for (int c0 = 0; c0 < CH; c0 += NB) {
+        if (DROP) {
+          unsigned long long blk[NB];
+          uint32_t o[NB][4];
+#pragma unroll
+          for (int q = 0; q < NB; ++q) blk[q] = blk0 + (unsigned)(lane + 32 * (c0 + q));
+          philox_blocks<NB>(blk, p.key, o);
+#pragma unroll
+          for (int q = 0; q < NB; ++q) masks_from_words<true>(p, o[q], km[c0 + q]);
+        } else {
+#pragma unroll
+          for (int q = 0; q < NB; ++q) masks_from_words<false>(p, km[c0 + q], km[c0 + q]);
+        }
+      }
+    }
     const int len = valid_length<EXT>(p, row);
     float m;
     if constexpr (HF) {
@@ -365,12 +417,11 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
     const float g = __fmul_rn(inv, p.keep_scale);
     const uint64_t g2 = pack2(g, g);
 
-    const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)L) >> 3;
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       if (valid[c]) {
         const long long off = row * L + (lane + 32 * c) * 8;
-        finish_unit<T, DROP>(e2[c], g2, out + off, p.mask + off, p, blk0 + (unsigned)(lane + 32 * c));
+        finish_unit_masked<T, DROP>(e2[c], g2, out + off, p.mask + off, km[c]);
       }
     }
 #pragma unroll
