@@ -139,6 +139,21 @@ typedef struct {
   float cpu_time_ms, total_time_ms;
 } TensorFuseMetrics;
 
+/* reference src/tensorfuse/types.h:226-253: carried for source compatibility;
+ * no entry point of either library reads them. */
+typedef struct {
+  int tile_m, tile_n, tile_k, warp_m, warp_n, warp_k, stages, split_k;
+} TensorFuseKernelConfig;
+
+typedef struct {
+  int max_iterations;
+  float time_limit_seconds;
+  int num_warmup_runs, num_timing_runs;
+  float relative_threshold;
+  bool use_heuristics, cache_results;
+  const char* cache_file;
+} TensorFuseAutotunerConfig;
+
 static inline size_t tensorfuse_sizeof_dtype(TensorFuseDataType t) {
   switch (t) {
     case TENSORFUSE_FLOAT32: case TENSORFUSE_INT32: return 4;
@@ -157,5 +172,47 @@ static inline size_t tensorfuse_tensor_size_bytes(const TensorFuseShape* s, Tens
 
 #ifdef __cplusplus
 }
+
+/* C++ spellings of the types above, and the two C++-only structures the
+ * namespace interface returns.  reference src/tensorfuse/types.h:293-332 */
+#include <string>
+namespace tensorfuse {
+using Status = TensorFuseStatus;
+using DataType = TensorFuseDataType;
+using Layout = TensorFuseLayout;
+using Activation = TensorFuseActivation;
+using Shape = TensorFuseShape;
+using Tensor = TensorFuseTensor;
+using Config = TensorFuseConfig;
+using ModelConfig = TensorFuseModelConfig;
+using TransformerParams = TensorFuseTransformerParams;
+using ProfileConfig = TensorFuseProfileConfig;
+using Metrics = TensorFuseMetrics;
+using KernelConfig = TensorFuseKernelConfig;
+using AutotunerConfig = TensorFuseAutotunerConfig;
+
+struct DeviceInfo {
+  int device_id;
+  std::string device_name;
+  int compute_capability_major;
+  int compute_capability_minor;
+  size_t total_global_memory;
+  int multiprocessor_count;
+  int max_threads_per_block;
+  size_t max_shared_memory_per_block;
+  bool supports_tensor_cores;
+  bool supports_fp16;
+  bool supports_bf16;
+  bool supports_fp8;
+};
+
+struct MemoryStats {
+  size_t total_allocated; /* bytes handed out by allocate_device and not yet returned */
+  size_t free_memory;     /* cudaMemGetInfo of the library's device                    */
+  size_t used_memory;
+  size_t peak_usage;      /* high-water mark of total_allocated                        */
+  size_t num_blocks;
+};
+}  // namespace tensorfuse
 #endif
 #endif /* TENSORFUSE_B200_TYPES_H_ */

@@ -206,6 +206,21 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_host(const void* input, void* o
                                                       unsigned char* dropout_mask, long long rows,
                                                       int row_len, int dtype, float dropout_prob,
                                                       unsigned long long seed);
+/* Concurrency of the two host-buffer operators above: they may be called from
+ * several threads; calls that use the same device are serialised (they share
+ * that device's staging buffers and streams).  tensorfuse_shutdown must not
+ * run while one of them is in flight.
+ *
+ * Weights that do not change between calls: register the host range of B (and
+ * of bias) once and the GEMM operator keeps one device copy per selected
+ * device instead of uploading it on every call (the reference's binding
+ * uploads every operand per call, src/python/core_bindings.cpp:402-461).
+ * The range must stay unmodified and allocated until it is invalidated;
+ * invalidate (NULL = every range) before changing or freeing the memory.
+ * Lookup is by the exact start address passed to the operator. */
+TensorFuseStatus tensorfuse_b200_register_weights(const void* host_ptr, size_t bytes);
+TensorFuseStatus tensorfuse_b200_invalidate_weights(const void* host_ptr);
+
 /* The same operator as tensorfuse_b200_softmax_dropout_host for callers that
  * must not allocate device memory -- a process whose device memory already
  * belongs to another allocator or sits at an MPS / MIG cap, or a serving thread
@@ -229,6 +244,24 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_host_noalloc(const void* input,
                                                               float dropout_prob,
                                                               unsigned long long seed,
                                                               cudaStream_t stream);
+/* Device selection of the reference's benchmark programs: cudaSetDevice and
+ * nothing else.  reference benchmarks/tensorfuse_wrappers.cpp:30-46 (compiled
+ * into those programs there; exported here so that they link against the
+ * library alone).  Only the value 0 of the status is portable: the benchmark
+ * header declares its own enumerators (benchmarks/tensorfuse_c_api.h:20-28). */
+TensorFuseStatus tensorfuse_simple_init(int device_id);
+void tensorfuse_simple_cleanup(void);
+
+/* Helpers of the Python binding, in place of its direct CUDA runtime calls
+ * (reference src/python/core_bindings.cpp:402-461, memory_bindings.cpp:46-61,
+ * core_bindings.cpp:830-838 -- the last two return constants there).
+ * kind: 1 host->device, 2 device->host, 3 device->device; synchronous. */
+TensorFuseStatus tensorfuse_b200_memcpy(void* dst, const void* src, size_t bytes, int kind);
+TensorFuseStatus tensorfuse_b200_mem_info(int device, size_t* free_bytes, size_t* total_bytes);
+/* device < 0: the current device.  Any output pointer may be NULL. */
+TensorFuseStatus tensorfuse_b200_device_info(int device, char* name, int name_capacity, int* cc_major,
+                                             int* cc_minor, size_t* total_memory, int* multiprocessors);
+
 /* Page-locked host memory for the calls above. */
 void* tensorfuse_b200_alloc_pinned(size_t bytes);
 void tensorfuse_b200_free_pinned(void* p);

@@ -102,6 +102,14 @@ def _load():
     sig("tensorfuse_b200_gemm_bias_gelu_host", i, [vp, vp, vp, vp, i, i, i, i, i, i, i, f, f])
     sig("tensorfuse_b200_softmax_dropout_host", i, [vp, vp, vp, ll, i, i, f, ull])
     sig("tensorfuse_b200_softmax_dropout_host_noalloc", i, [vp, vp, vp, ll, i, i, f, ull, st])
+    sig("tensorfuse_b200_register_weights", i, [vp, C.c_size_t])
+    sig("tensorfuse_b200_invalidate_weights", i, [vp])
+    sig("tensorfuse_simple_init", i, [i])
+    sig("tensorfuse_simple_cleanup", None, [])
+    sig("tensorfuse_b200_memcpy", i, [vp, vp, C.c_size_t, i])
+    sig("tensorfuse_b200_mem_info", i, [i, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)])
+    sig("tensorfuse_b200_device_info", i, [i, C.c_char_p, i, C.POINTER(i), C.POINTER(i), C.POINTER(C.c_size_t),
+                                           C.POINTER(i)])
     sig("tensorfuse_b200_alloc_pinned", vp, [C.c_size_t])
     sig("tensorfuse_b200_free_pinned", None, [vp])
     sig("tensorfuse_b200_plan_shards", None, [ll, i, i, C.POINTER(ll), C.POINTER(ll)])

@@ -22,7 +22,7 @@ OBJDIR = os.path.join(PKG, "build")
 LIB = os.path.join(LIBDIR, "libtensorfuse.so")
 
 SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "quantize.cu", "layernorm.cu", "transformer_layer.cpp", "runtime.cpp", "c_api.cpp",
-           "host_ops.cpp", "noalloc.cu", "profiler.cpp"]
+           "host_ops.cpp", "noalloc.cu", "profiler.cpp", "cxx_api.cpp"]
 HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh", "gemm_tc_pair_kernel.cuh", "attention_tc_kernel.cuh", "philox.cuh", "tma_host.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -45,9 +45,8 @@ def is_stale() -> bool:
     if not os.path.exists(LIB):
         return True
     deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    deps += [os.path.join(ROOT, "include", "tensorfuse_b200.h"),
-             os.path.join(ROOT, "include", "tensorfuse", "types.h"),
-             os.path.join(ROOT, "include", "tensorfuse", "tensorfuse.h")]
+    deps += [os.path.join(ROOT, "include", "tensorfuse_b200.h"), os.path.join(ROOT, "include", "tensorfuse.h")]
+    deps += [os.path.join(ROOT, "include", "tensorfuse", f) for f in ("types.h", "tensorfuse.h", "kernels.h", "profiler.h")]
     return _newest(deps) > os.path.getmtime(LIB)
 
 

@@ -9,6 +9,7 @@
 
 #include "kernels.h"
 #include "runtime.h"
+#include "tensorfuse/kernels.h"
 #include "tensorfuse/tensorfuse.h"
 #include "tensorfuse_b200.h"
 
@@ -381,6 +382,8 @@ TensorFuseStatus tensorfuse_allocate_tensor(TensorFuseTensor* tensor, const Tens
   if (!Runtime::get().initialized()) return TENSORFUSE_ERROR_NOT_INITIALIZED;
   if (!tensor || !shape) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
   if (shape->ndims < 0 || shape->ndims > TENSORFUSE_MAX_DIMS) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
+  for (int i = 0; i < shape->ndims; ++i)
+    if (shape->dims[i] < 0) return TENSORFUSE_ERROR_INVALID_TENSOR_SHAPE;
   const size_t bytes = tensorfuse_tensor_size_bytes(shape, dtype);
   void* data = nullptr;
   DeviceGuard g(device_id);

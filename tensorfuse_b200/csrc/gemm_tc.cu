@@ -228,6 +228,9 @@ LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
 }
 
 LaunchResult launch_gemm(const GemmArgs& a, cudaStream_t stream) {
+  // the epilogues read the bias as FP32, FP16 or BF16 and nothing else
+  if (a.epilogue != kEpiI8Raw && a.bias_dtype != kF32 && a.bias_dtype != kF16 && a.bias_dtype != kBF16)
+    return kUnsupported;
   if (gemm_tc_eligible(a)) return launch_gemm_tc(a, stream);
   return launch_gemm_simt(a, stream);
 }

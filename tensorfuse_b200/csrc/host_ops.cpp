@@ -11,6 +11,16 @@
 //   s_out     device -> host copy of chunk i (waits for the kernel)
 // so that the copies in both directions overlap each other and the kernels.
 // Staging buffers are grow-only and live until tensorfuse_shutdown.
+//
+// Concurrency: a call holds the mutex of every device context it uses from its
+// first reservation to its final synchronisation, so host-buffer calls from
+// several threads are serialised per device (they share the staging buffers,
+// streams and events).  On any failure the three streams are drained before
+// the call returns, so the caller's buffers are never written afterwards.
+//
+// Weights: B and bias are uploaded on every call unless the caller has
+// registered the host range as immutable (tensorfuse_b200_register_weights);
+// then each device keeps one copy until tensorfuse_b200_invalidate_weights.
 #include <algorithm>
 #include <thread>
 #include <utility>
@@ -68,11 +78,42 @@ struct GemmHostJob {
   const char* A; const char* B; const char* bias; char* C;
   int N, K, in_dtype, bias_dtype, out_dtype, epilogue;
   float scale;
+  bool b_static, bias_static;   // registered as immutable: one cached device copy per device
 };
+
+// Drains the three streams of a context: after a failure nothing may still be
+// writing the caller's buffers when the (blocking) operator returns.
+void drain(DeviceCtx* cx) {
+  if (!cx->ready) return;
+  cudaStreamSynchronize(cx->s_in);
+  cudaStreamSynchronize(cx->s_compute);
+  cudaStreamSynchronize(cx->s_out);
+  cudaGetLastError();
+}
+
+// Device copy of a registered host range, uploaded on s_in the first time it is seen.
+TensorFuseStatus cached_weight(DeviceCtx* cx, const void* host, size_t bytes, void** dev) {
+  DevBuffer& buf = cx->weights[host];
+  if (buf.ptr == nullptr || buf.cap < bytes) {
+    CK(buf.reserve(bytes));
+    CK(cudaMemcpyAsync(buf.ptr, host, bytes, cudaMemcpyHostToDevice, cx->s_in));
+  }
+  *dev = buf.ptr;
+  return TENSORFUSE_SUCCESS;
+}
+
+TensorFuseStatus gemm_shard_locked(DeviceCtx* cx, const GemmHostJob& j, long long row0, long long rows);
 
 TensorFuseStatus gemm_shard(DeviceCtx* cx, const GemmHostJob& j, long long row0, long long rows) {
   if (rows <= 0) return TENSORFUSE_SUCCESS;
+  std::lock_guard<std::mutex> lk(cx->mu);
   DeviceGuard dg(cx->id);
+  const TensorFuseStatus st = gemm_shard_locked(cx, j, row0, rows);
+  if (st != TENSORFUSE_SUCCESS) drain(cx);
+  return st;
+}
+
+TensorFuseStatus gemm_shard_locked(DeviceCtx* cx, const GemmHostJob& j, long long row0, long long rows) {
   const size_t es = dtype_size(j.in_dtype), bs = dtype_size(j.bias_dtype), os = dtype_size(j.out_dtype);
   const size_t a_row = (size_t)j.K * es, c_row = (size_t)j.N * os;
   // Chunks of about 16 MB of traffic, but the first ones are small (256 rows, doubling): the
@@ -89,11 +130,24 @@ TensorFuseStatus gemm_shard(DeviceCtx* cx, const GemmHostJob& j, long long row0,
   CK(cx->ensure(nchunks));
   CK(cx->a.reserve((size_t)rows * a_row));
   CK(cx->c.reserve((size_t)rows * c_row));
-  CK(cx->b.reserve((size_t)j.K * j.N * es));
-  CK(cx->bias.reserve(std::max<size_t>((size_t)j.N * bs, 16)));
-
-  CK(cudaMemcpyAsync(cx->b.ptr, j.B, (size_t)j.K * j.N * es, cudaMemcpyHostToDevice, cx->s_in));
-  if (j.bias) CK(cudaMemcpyAsync(cx->bias.ptr, j.bias, (size_t)j.N * bs, cudaMemcpyHostToDevice, cx->s_in));
+  void* dB = nullptr;
+  void* dBias = nullptr;
+  if (j.b_static) {
+    const TensorFuseStatus st = cached_weight(cx, j.B, (size_t)j.K * j.N * es, &dB);
+    if (st != TENSORFUSE_SUCCESS) return st;
+  } else {
+    CK(cx->b.reserve((size_t)j.K * j.N * es));
+    CK(cudaMemcpyAsync(cx->b.ptr, j.B, (size_t)j.K * j.N * es, cudaMemcpyHostToDevice, cx->s_in));
+    dB = cx->b.ptr;
+  }
+  if (j.bias && j.bias_static) {
+    const TensorFuseStatus st = cached_weight(cx, j.bias, (size_t)j.N * bs, &dBias);
+    if (st != TENSORFUSE_SUCCESS) return st;
+  } else {
+    CK(cx->bias.reserve(std::max<size_t>((size_t)j.N * bs, 16)));
+    if (j.bias) CK(cudaMemcpyAsync(cx->bias.ptr, j.bias, (size_t)j.N * bs, cudaMemcpyHostToDevice, cx->s_in));
+    dBias = cx->bias.ptr;
+  }
   CK(cudaEventRecord(cx->ev_weights, cx->s_in));
   CK(cudaStreamWaitEvent(cx->s_compute, cx->ev_weights, 0));
 
@@ -107,13 +161,13 @@ TensorFuseStatus gemm_shard(DeviceCtx* cx, const GemmHostJob& j, long long row0,
     CK(cudaEventRecord(cx->ev_in[i], cx->s_in));
     CK(cudaStreamWaitEvent(cx->s_compute, cx->ev_in[i], 0));
     GemmArgs g{};
-    g.A = dA; g.B = cx->b.ptr; g.bias = cx->bias.ptr; g.C = dC;
+    g.A = dA; g.B = dB; g.bias = dBias; g.C = dC;
     g.M = (int)nr; g.N = j.N; g.K = j.K;
     g.in_dtype = j.in_dtype; g.bias_dtype = j.bias_dtype; g.out_dtype = j.out_dtype;
     g.epilogue = j.epilogue;
     g.alpha = 1.0f; g.beta = 1.0f; g.scale = j.scale;
     const LaunchResult lr = launch_gemm(g, cx->s_compute);
-    if (lr != kOk) { cudaDeviceSynchronize(); return from_launch(lr); }
+    if (lr != kOk) return from_launch(lr);
     CK(cudaEventRecord(cx->ev_done[i], cx->s_compute));
     CK(cudaStreamWaitEvent(cx->s_out, cx->ev_done[i], 0));
     CK(cudaMemcpyAsync(j.C + (size_t)(row0 + r0) * c_row, dC, (size_t)nr * c_row,
@@ -128,9 +182,18 @@ struct SoftmaxHostJob {
   int L, dtype; float p; unsigned long long seed;
 };
 
+TensorFuseStatus softmax_shard_locked(DeviceCtx* cx, const SoftmaxHostJob& j, long long row0, long long rows);
+
 TensorFuseStatus softmax_shard(DeviceCtx* cx, const SoftmaxHostJob& j, long long row0, long long rows) {
   if (rows <= 0) return TENSORFUSE_SUCCESS;
+  std::lock_guard<std::mutex> lk(cx->mu);
   DeviceGuard dg(cx->id);
+  const TensorFuseStatus st = softmax_shard_locked(cx, j, row0, rows);
+  if (st != TENSORFUSE_SUCCESS) drain(cx);
+  return st;
+}
+
+TensorFuseStatus softmax_shard_locked(DeviceCtx* cx, const SoftmaxHostJob& j, long long row0, long long rows) {
   const size_t es = dtype_size(j.dtype);
   const size_t row_b = (size_t)j.L * es;
   const long long chunk = rows_per_chunk(2 * row_b + (size_t)j.L, size_t(16) << 20, 16);
@@ -151,7 +214,7 @@ TensorFuseStatus softmax_shard(DeviceCtx* cx, const SoftmaxHostJob& j, long long
     CK(cudaStreamWaitEvent(cx->s_compute, cx->ev_in[i], 0));
     const LaunchResult lr = launch_softmax_dropout(dI, dO, dM, nr, j.L, j.dtype, j.p, j.seed,
                                                    (unsigned long long)(row0 + r0), cx->s_compute);
-    if (lr != kOk) { cudaDeviceSynchronize(); return from_launch(lr); }
+    if (lr != kOk) return from_launch(lr);
     CK(cudaEventRecord(cx->ev_done[i], cx->s_compute));
     CK(cudaStreamWaitEvent(cx->s_out, cx->ev_done[i], 0));
     CK(cudaMemcpyAsync(j.out + (size_t)(row0 + r0) * row_b, dO, (size_t)nr * row_b,
@@ -219,6 +282,9 @@ TensorFuseStatus tensorfuse_b200_gemm_bias_gelu_host(const void* A, const void* 
     return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION;
   }
   if (!bias && j.epilogue != kEpiI8Raw) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  // looked up before any device context is locked (lock order: runtime, then context)
+  j.b_static = Runtime::get().registered_bytes(B) >= (size_t)K * N * dtype_size(in_dtype);
+  j.bias_static = bias && Runtime::get().registered_bytes(bias) >= (size_t)N * dtype_size(j.bias_dtype);
   return for_each_shard(M, 128, [&](DeviceCtx* cx, long long b, long long c) {
     return gemm_shard(cx, j, b, c);
   });
@@ -239,6 +305,19 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_host(const void* input, void* o
   return for_each_shard(rows, 16, [&](DeviceCtx* cx, long long b, long long c) {
     return softmax_shard(cx, j, b, c);
   });
+}
+
+TensorFuseStatus tensorfuse_b200_register_weights(const void* host_ptr, size_t bytes) {
+  if (!Runtime::get().initialized()) return TENSORFUSE_ERROR_NOT_INITIALIZED;
+  if (!host_ptr || bytes == 0) return TENSORFUSE_ERROR_INVALID_ARGUMENT;
+  Runtime::get().register_weights(host_ptr, bytes);
+  return TENSORFUSE_SUCCESS;
+}
+
+TensorFuseStatus tensorfuse_b200_invalidate_weights(const void* host_ptr) {
+  if (!Runtime::get().initialized()) return TENSORFUSE_ERROR_NOT_INITIALIZED;
+  Runtime::get().invalidate_weights(host_ptr);
+  return TENSORFUSE_SUCCESS;
 }
 
 void* tensorfuse_b200_alloc_pinned(size_t bytes) {

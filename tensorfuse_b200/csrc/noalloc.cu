@@ -93,6 +93,9 @@ extern "C" TensorFuseStatus tensorfuse_b200_softmax_dropout_host_noalloc(
   if (cudaMemcpyAsync(output, d_out, elems * es, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
       cudaMemcpyAsync(dropout_mask, d_mask, elems, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
       cudaStreamSynchronize(stream) != cudaSuccess) {
+    // whatever was enqueued before the failure must not still be using the shared
+    // staging area, or writing the caller's buffers, once this call has returned
+    cudaStreamSynchronize(stream);
     cudaGetLastError();
     return TENSORFUSE_ERROR_CUDA_ERROR;
   }

@@ -46,9 +46,11 @@ cudaError_t DeviceCtx::ensure(size_t chunks) {
 }
 
 void DeviceCtx::destroy() {
-  if (!ready && !a.ptr && !b.ptr && !bias.ptr && !c.ptr && !mask.ptr) return;
+  if (!ready && !a.ptr && !b.ptr && !bias.ptr && !c.ptr && !mask.ptr && weights.empty()) return;
   DeviceGuard g(id);
   a.release(); b.release(); bias.release(); c.release(); mask.release();
+  for (auto& kv : weights) kv.second.release();
+  weights.clear();
   for (cudaEvent_t e : ev_in) cudaEventDestroy(e);
   for (cudaEvent_t e : ev_done) cudaEventDestroy(e);
   ev_in.clear(); ev_done.clear();
@@ -100,8 +102,11 @@ TensorFuseStatus Runtime::init(const TensorFuseConfig* cfg) {
   }
   cfg_.device_ids = nullptr;  // the caller's array is not retained
   devices_ = devs;
-  ctxs_.assign(devs.size(), DeviceCtx());
-  for (size_t i = 0; i < devs.size(); ++i) ctxs_[i].id = devs[i];
+  ctxs_.clear();
+  for (size_t i = 0; i < devs.size(); ++i) {
+    ctxs_.emplace_back(new DeviceCtx());
+    ctxs_[i]->id = devs[i];
+  }
   initialized_ = true;
   return TENSORFUSE_SUCCESS;
 }
@@ -109,8 +114,19 @@ TensorFuseStatus Runtime::init(const TensorFuseConfig* cfg) {
 TensorFuseStatus Runtime::shutdown() {
   std::lock_guard<std::mutex> g(mu_);
   if (!initialized_) return TENSORFUSE_SUCCESS;
-  for (DeviceCtx& c : ctxs_) c.destroy();
+  for (auto& c : ctxs_) {
+    std::lock_guard<std::mutex> lk(c->mu);   // a host-buffer call still in flight finishes first
+    c->destroy();
+  }
   ctxs_.clear();
+  static_weights_.clear();
+  for (auto& kv : pools_) {
+    DeviceGuard dg(kv.first);
+    cudaDeviceSynchronize();           // stream-ordered frees into the pool have completed
+    cudaMemPoolDestroy(kv.second);
+  }
+  pools_.clear();
+  cudaGetLastError();
   devices_.clear();
   initialized_ = false;
   return TENSORFUSE_SUCCESS;
@@ -130,7 +146,55 @@ std::vector<int> Runtime::devices() {
 }
 DeviceCtx* Runtime::ctx(size_t i) {
   std::lock_guard<std::mutex> g(mu_);
-  return i < ctxs_.size() ? &ctxs_[i] : nullptr;
+  return i < ctxs_.size() ? ctxs_[i].get() : nullptr;
+}
+
+cudaMemPool_t Runtime::workspace_pool(int device) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = pools_.find(device);
+  if (it != pools_.end()) return it->second;
+  cudaMemPoolProps props{};
+  props.allocType = cudaMemAllocationTypePinned;
+  props.handleTypes = cudaMemHandleTypeNone;
+  props.location.type = cudaMemLocationTypeDevice;
+  props.location.id = device;
+  cudaMemPool_t pool = nullptr;
+  if (cudaMemPoolCreate(&pool, &props) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  unsigned long long threshold = ~0ull;
+  cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold);
+  cudaGetLastError();
+  pools_[device] = pool;
+  return pool;
+}
+
+void Runtime::register_weights(const void* host_ptr, size_t bytes) {
+  std::lock_guard<std::mutex> g(mu_);
+  if (host_ptr && bytes) static_weights_[host_ptr] = bytes;
+}
+size_t Runtime::registered_bytes(const void* host_ptr) {
+  std::lock_guard<std::mutex> g(mu_);
+  auto it = static_weights_.find(host_ptr);
+  return it == static_weights_.end() ? 0 : it->second;
+}
+void Runtime::invalidate_weights(const void* host_ptr) {
+  std::vector<DeviceCtx*> ctxs;
+  {
+    std::lock_guard<std::mutex> g(mu_);
+    if (host_ptr) static_weights_.erase(host_ptr);
+    else static_weights_.clear();
+    for (auto& c : ctxs_) ctxs.push_back(c.get());
+  }
+  for (DeviceCtx* c : ctxs) {
+    std::lock_guard<std::mutex> lk(c->mu);   // no call is using the copies while they are dropped
+    DeviceGuard dg(c->id);
+    if (host_ptr) {
+      auto it = c->weights.find(host_ptr);
+      if (it != c->weights.end()) { it->second.release(); c->weights.erase(it); }
+    } else {
+      for (auto& kv : c->weights) kv.second.release();
+      c->weights.clear();
+    }
+  }
 }
 
 static inline unsigned long long splitmix64(unsigned long long x) {

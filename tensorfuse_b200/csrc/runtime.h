@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
+#include <memory>
 #include <mutex>
 #include <vector>
 
@@ -25,9 +27,15 @@ struct DevBuffer {
   void release();
 };
 
+// Per-device state of the host-buffer operators.  One call at a time may use
+// it: the operators hold `mu` from the first reservation to the final
+// synchronisation, so concurrent callers are serialised per device.
 struct DeviceCtx {
   int id = 0;
   bool ready = false;
+  std::mutex mu;
+  // device copies of host weight ranges registered as immutable, keyed by host address
+  std::map<const void*, DevBuffer> weights;
   cudaStream_t s_in = nullptr, s_compute = nullptr, s_out = nullptr;
   std::vector<cudaEvent_t> ev_in, ev_done;  // one pair per in-flight chunk
   cudaEvent_t ev_weights = nullptr;
@@ -46,6 +54,18 @@ class Runtime {
   std::vector<int> devices();
   DeviceCtx* ctx(size_t i);  // i-th selected device; contexts are created lazily
 
+  // Host ranges the caller has declared immutable: the host-buffer operators
+  // keep one device copy per selected device instead of uploading per call.
+  void register_weights(const void* host_ptr, size_t bytes);
+  void invalidate_weights(const void* host_ptr);   // null: all of them
+  size_t registered_bytes(const void* host_ptr);   // 0 when not registered
+
+  // Stream-ordered workspace pool owned by the library, one per device, created
+  // on first use and destroyed at shutdown.  Its release threshold is unlimited,
+  // so workspace freed by one call is reused by the next without a trip to the
+  // driver; the device's default pool (shared with the host process) is left alone.
+  cudaMemPool_t workspace_pool(int device);
+
   void set_seed(unsigned long long seed);
   unsigned long long next_seed();
 
@@ -54,7 +74,9 @@ class Runtime {
   bool initialized_ = false;
   TensorFuseConfig cfg_{};
   std::vector<int> devices_;
-  std::vector<DeviceCtx> ctxs_;
+  std::vector<std::unique_ptr<DeviceCtx>> ctxs_;
+  std::map<const void*, size_t> static_weights_;   // registered host ranges: address -> bytes
+  std::map<int, cudaMemPool_t> pools_;
   bool seeded_ = false;
   unsigned long long seed_base_ = 0, seed_calls_ = 0;
 };

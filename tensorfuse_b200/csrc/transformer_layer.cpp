@@ -32,22 +32,6 @@ bool is_vector(const TensorFuseTensor* t, int n, TensorFuseDataType dt) {
   return t && t->data && t->shape.ndims == 1 && t->shape.dims[0] == n && t->dtype == dt;
 }
 
-// The workspace comes from the device's default stream-ordered pool.  Left at its
-// default the pool hands freed memory back to the driver at the next
-// synchronisation and the following call pays for mapping it again (milliseconds
-// at BERT-large sizes); raising the release threshold once keeps it cached.
-void keep_pool_cached(int dev) {
-  static bool done[64] = {};
-  if (dev < 0 || dev >= 64 || done[dev]) return;
-  cudaMemPool_t pool = nullptr;
-  if (cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess && pool != nullptr) {
-    unsigned long long threshold = ~0ull;
-    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &threshold);
-  }
-  cudaGetLastError();
-  done[dev] = true;
-}
-
 LaunchResult gemm(const void* A, const void* B, const void* bias, void* C, int M, int N, int K, int dt, int epi,
                   float beta, cudaStream_t stream) {
   GemmArgs a{};
@@ -104,13 +88,18 @@ extern "C" TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseT
 
   const int dev = device_of_pointer(output->data);
   DeviceGuard guard(dev);
-  keep_pool_cached(dev);
+  // workspace from the library's own stream-ordered pool (kept cached between calls)
+  int pool_dev = dev;
+  if (pool_dev < 0) cudaGetDevice(&pool_dev);
+  cudaMemPool_t pool = Runtime::get().workspace_pool(pool_dev);
+  if (pool == nullptr) return TENSORFUSE_ERROR_OUT_OF_MEMORY;
   auto round_up = [](size_t v) { return (v + 255) & ~(size_t)255; };
   const size_t mh = round_up((size_t)M * H * es), mf = round_up((size_t)M * F * es);
   const size_t wcat_bytes = round_up((size_t)3 * H * H * es);
   const size_t bcat_bytes = round_up((size_t)(3 * H > F ? 3 * H : F) * es);
   char* ws = nullptr;
-  if (cudaMallocAsync(reinterpret_cast<void**>(&ws), 4 * mh + mf + wcat_bytes + bcat_bytes, stream) != cudaSuccess) {
+  if (cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), 4 * mh + mf + wcat_bytes + bcat_bytes, pool, stream) !=
+      cudaSuccess) {
     cudaGetLastError();
     return TENSORFUSE_ERROR_OUT_OF_MEMORY;
   }

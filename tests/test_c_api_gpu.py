@@ -141,3 +141,23 @@ def test_python_api_paths(tf, oracle):
     assert oracle.f16_parity_violations(o16, want16) == 0
     with pytest.raises(RuntimeError, match="Invalid tensor shape"):
         tf.fused_gemm_bias_gelu(x, w[:, :8], b)
+
+
+def test_config1_full_size_through_the_struct_entry(tf, oracle):
+    """Benchmark configuration 1 exactly: X[32,128,768] ~ N(0,1), W[768,3072] ~ N(0,1/768),
+    b ~ N(0, 0.02^2), seed 0, FP32, 3-D tensors through tensorfuse_fused_gemm_bias_gelu; the
+    whole output against the CPU loop at the reference's tolerance
+    (reference src/tests/test_kernels.cu:139: max abs error < 1e-4)."""
+    from gpu_util import L, byref, c_tensor, check_watchdog, dev, host, stream
+    from tensorfuse_b200 import workloads
+    x, w, b = workloads.gemm_fp32_quickstart()
+    assert x.shape == (32, 128, 768) and w.shape == (768, 3072) and b.shape == (3072,)
+    dx, dw, db = dev(x), dev(w), dev(b)
+    out = torch.full((32, 128, 3072), float("nan"), dtype=torch.float32, device="cuda")
+    ti, tw, tb, to = c_tensor(dx), c_tensor(dw), c_tensor(db), c_tensor(out)
+    assert L.tensorfuse_fused_gemm_bias_gelu(byref(ti), byref(tw), byref(tb), byref(to), stream()) == 0
+    check_watchdog()
+    got = host(out).reshape(-1, 3072)
+    want = oracle.gemm_bias_gelu_f32(x.reshape(-1, 768), w, b)
+    assert np.isfinite(got).all()
+    assert float(np.max(np.abs(got - want))) < 1e-4

@@ -65,3 +65,34 @@ def test_bad_device_list_is_rejected_without_launching(tf):
             t.init(t.Config(device_ids=[0, 0]))
     finally:
         t.init()
+
+
+def test_registered_weights_are_uploaded_once(tf, oracle):
+    """A weight range registered as immutable is copied to the device on first use
+    only: changing the host bytes afterwards (without invalidating) must not
+    change the result, and invalidating must."""
+    from tensorfuse_b200 import workloads
+    from tensorfuse_b200._lib import lib as L
+    A, B, b = workloads.gemm_fp16_ffn(seed=8, M=640, K=256, N=512)
+    B = np.ascontiguousarray(B); b = np.ascontiguousarray(b)
+    first = tf.fused_gemm_bias_gelu(A, B, b)
+    assert L.tensorfuse_b200_register_weights(B.ctypes.data, B.nbytes) == 0
+    assert L.tensorfuse_b200_register_weights(b.ctypes.data, b.nbytes) == 0
+    assert L.tensorfuse_b200_register_weights(None, 4) == 1
+    try:
+        cached = tf.fused_gemm_bias_gelu(A, B, b)                  # uploads and caches
+        assert np.array_equal(cached.view(np.uint16), first.view(np.uint16))
+        B_saved = B.copy()
+        B[...] = 0                                                 # the device copy is still the old one
+        stale = tf.fused_gemm_bias_gelu(A, B, b)
+        assert np.array_equal(stale.view(np.uint16), first.view(np.uint16))
+        assert L.tensorfuse_b200_invalidate_weights(B.ctypes.data) == 0
+        fresh = tf.fused_gemm_bias_gelu(A, B, b)                   # B is all zero now: gelu(bias) everywhere
+        want = oracle.gemm_bias_gelu_f16(A, B, b)
+        assert oracle.f16_parity_violations(fresh, want) == 0
+        assert not np.array_equal(fresh.view(np.uint16), first.view(np.uint16))
+        B[...] = B_saved
+    finally:
+        assert L.tensorfuse_b200_invalidate_weights(None) == 0
+    again = tf.fused_gemm_bias_gelu(A, B, b)
+    assert np.array_equal(again.view(np.uint16), first.view(np.uint16))
