@@ -181,6 +181,10 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_rows(const void* input, void* o
  * elements (vec = elements per thread step, warps = warps per row); a CPU that
  * follows the same schedule reproduces the result bit for bit. */
 void tensorfuse_b200_softmax_schedule(int row_len, int dtype, int aligned16, int* vec, int* warps);
+/* The same with the third property of the schedule: online = 1 for rows too
+ * long to be held in shared memory (more than 200 KiB), whose sum of
+ * exponentials is formed in a single sweep with a running maximum. */
+void tensorfuse_b200_softmax_schedule_ex(int row_len, int dtype, int aligned16, int* vec, int* warps, int* online);
 
 /* Seed source of tensorfuse_fused_softmax_dropout: after this call the n-th
  * dropout call uses a seed derived from (seed, n).  Declared, but a no-op, in
@@ -217,7 +221,11 @@ TensorFuseStatus tensorfuse_b200_softmax_dropout_host(const void* input, void* o
  * uploads every operand per call, src/python/core_bindings.cpp:402-461).
  * The range must stay unmodified and allocated until it is invalidated;
  * invalidate (NULL = every range) before changing or freeing the memory.
- * Lookup is by the exact start address passed to the operator. */
+ * Lookup is by the exact start address passed to the operator.
+ * Device memory may be registered too: tensorfuse_fused_transformer_layer then
+ * builds its fused [hidden, 3*hidden] query/key/value weight (and bias) once per
+ * device for a layer whose three projection matrices are registered, instead of
+ * concatenating them on every call. */
 TensorFuseStatus tensorfuse_b200_register_weights(const void* host_ptr, size_t bytes);
 TensorFuseStatus tensorfuse_b200_invalidate_weights(const void* host_ptr);
 

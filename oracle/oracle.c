@@ -350,14 +350,94 @@ static void softmax_row_exact(const float* x, float* y, int L, int vec, int warp
   for (int j = 0; j < L; ++j) y[j] = y[j] * g;
 }
 
+/* One row, online form: the schedule of the library's kernel for rows that do
+ * not fit in shared memory (tensorfuse_b200/csrc/softmax_dropout.cu,
+ * softmax_online_kernel).  Thread t of T = 32*warps owns the units t, t+T, ...
+ * (V = vec consecutive elements each) and keeps a running maximum m_t and two
+ * partial sums (even / odd position inside the unit) relative to it: a unit
+ * whose maximum mu exceeds m_t first multiplies both sums by
+ * 2^(max(fma(m_t, log2e, -(mu*log2e)), -127)); a unit that is all -inf is
+ * skipped.  At the end every thread's sum s0+s1 is multiplied by
+ * 2^(max(fma(m_t, log2e, -(m*log2e)), -127)) with m the row maximum (0 for a
+ * thread that saw nothing), lanes combine by the xor butterfly, warps in
+ * ascending order.  FP32-storage exponential for both storage types. */
+static void softmax_row_online(const float* x, float* y, int L, int vec, int warps, float keep_scale) {
+  const float LOG2E = 0x1.715476p+0f;
+  const int T = 32 * warps;
+  const int units = (L + vec - 1) / vec;
+  float lane_m[32 * 32], lane_s[32 * 32];
+  float mx = -INFINITY;
+  for (int t = 0; t < T; ++t) {
+    float mt = -INFINITY, s0 = 0.0f, s1 = 0.0f, negc = 0.0f;
+    for (int u = t; u < units; u += T) {
+      const int j0 = u * vec, j1 = j0 + vec < L ? j0 + vec : L;
+      float mu = -INFINITY;
+      for (int j = j0; j < j1; ++j) mu = fmaxf(mu, x[j]);
+      if (mu == -INFINITY) continue;
+      if (mu > mt) {
+        const float nc = -(mu * LOG2E);
+        if (mt != -INFINITY) {
+          const float f = exp2_poly(fmaxf(fmaf(mt, LOG2E, nc), -127.0f));
+          s0 *= f; s1 *= f;
+        }
+        mt = mu; negc = nc;
+      }
+      for (int j = j0; j < j1; ++j) {
+        const float e = exp2_poly(fmaxf(fmaf(x[j], LOG2E, negc), -127.0f));
+        if ((j - j0) & 1) s1 += e; else s0 += e;
+      }
+    }
+    lane_m[t] = mt; lane_s[t] = s0 + s1;
+    mx = fmaxf(mx, mt);
+  }
+  const int all_masked = mx == -INFINITY;
+  if (all_masked) mx = 0.0f;
+  const float negc = -(mx * LOG2E);
+  float total = 0.0f;
+  for (int w = 0; w < warps; ++w) {
+    float v[32];
+    for (int l = 0; l < 32; ++l) {
+      const int t = 32 * w + l;
+      v[l] = lane_m[t] == -INFINITY ? 0.0f
+                                    : lane_s[t] * exp2_poly(fmaxf(fmaf(lane_m[t], LOG2E, negc), -127.0f));
+    }
+    for (int off = 16; off >= 1; off >>= 1) {
+      float nv[32];
+      for (int l = 0; l < 32; ++l) nv[l] = v[l] + v[l ^ off];
+      memcpy(v, nv, sizeof(v));
+    }
+    total = (w == 0) ? v[0] : total + v[0];
+  }
+  const float inv = (total == 0.0f || all_masked) ? 0.0f : 1.0f / total;
+  const float g = inv * keep_scale;
+  for (int j = 0; j < L; ++j) y[j] = exp2_poly(fmaxf(fmaf(x[j], LOG2E, negc), -127.0f)) * g;
+}
+
 static inline float keep_scale_of(float p) { return p >= 1.0f ? 0.0f : 1.0f / (1.0f - p); }
 
 /* dtype: 0 = FP32 storage, 1 = FP16 storage.  first_row offsets the Philox
  * element index so that a shard of a larger tensor reproduces the mask of the
  * whole. */
+static void softmax_dropout_exact_impl(const void* in, void* out, uint8_t* mask, long rows, int L,
+                                       int dtype, float p, uint64_t seed, uint64_t first_row, int vec,
+                                       int warps, int online, int threads);
+
 void tfo_softmax_dropout_exact(const void* in, void* out, uint8_t* mask, long rows, int L,
                                int dtype, float p, uint64_t seed, uint64_t first_row, int vec,
                                int warps, int threads) {
+  softmax_dropout_exact_impl(in, out, mask, rows, L, dtype, p, seed, first_row, vec, warps, 0, threads);
+}
+
+/* The same with the online schedule (softmax_row_online). */
+void tfo_softmax_dropout_exact_online(const void* in, void* out, uint8_t* mask, long rows, int L,
+                                      int dtype, float p, uint64_t seed, uint64_t first_row, int vec,
+                                      int warps, int threads) {
+  softmax_dropout_exact_impl(in, out, mask, rows, L, dtype, p, seed, first_row, vec, warps, 1, threads);
+}
+
+static void softmax_dropout_exact_impl(const void* in, void* out, uint8_t* mask, long rows, int L,
+                                       int dtype, float p, uint64_t seed, uint64_t first_row, int vec,
+                                       int warps, int online, int threads) {
   set_threads(threads);
   const uint32_t thr = tfo_dropout_threshold(p);
   const float ks = keep_scale_of(p);
@@ -373,7 +453,8 @@ void tfo_softmax_dropout_exact(const void* in, void* out, uint8_t* mask, long ro
       } else {
         memcpy(x, (const float*)in + r * L, sizeof(float) * (size_t)L);
       }
-      softmax_row_exact(x, y, L, vec, warps, ks, dtype == 1);
+      if (online) softmax_row_online(x, y, L, vec, warps, ks);
+      else softmax_row_exact(x, y, L, vec, warps, ks, dtype == 1);
       for (int j = 0; j < L; ++j) {
         uint64_t idx = (first_row + (uint64_t)r) * (uint64_t)L + (uint64_t)j;
         int keep = thr == 0 ? 1 : dropout_keep(idx, seed, thr);

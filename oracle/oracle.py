@@ -59,6 +59,7 @@ def lib():
         L.tfo_dropout_threshold.argtypes = [f]
         L.tfo_dropout_mask.argtypes = [vp, u64, l, f, u64]
         L.tfo_softmax_dropout_exact.argtypes = [vp, vp, vp, l, i, i, f, u64, u64, i, i, i]
+        L.tfo_softmax_dropout_exact_online.argtypes = [vp, vp, vp, l, i, i, f, u64, u64, i, i, i]
         L.tfo_softmax_dropout_exact_ext.argtypes = [vp, vp, vp, l, i, i, f, u64, i, i, f, vp, l, i]
         L.tfo_attention_f32.argtypes = [vp, vp, vp, vp, i, i, i, i, i, f, f, u64, vp, i]
         _lib = L
@@ -158,21 +159,21 @@ def dropout_mask(n, p, seed, first_idx=0):
     return m
 
 
-def softmax_dropout_exact(x, p=0.0, seed=0, first_row=0, vec=8, warps=1, threads=0):
+def softmax_dropout_exact(x, p=0.0, seed=0, first_row=0, vec=8, warps=1, threads=0, online=False):
     """Bit-reproducible softmax+dropout over the last axis.
 
-    ``vec``/``warps`` name the summation schedule (see oracle.c); the library
-    reports the schedule it uses for a given row length and dtype through
-    ``tensorfuse_b200_softmax_schedule``.
+    ``vec``/``warps``/``online`` name the summation schedule (see oracle.c); the
+    library reports the schedule it uses for a given row length and dtype through
+    ``tensorfuse_b200_softmax_schedule_ex``.
     """
     assert x.dtype in (np.float16, np.float32)
     x = np.ascontiguousarray(x)
     L = x.shape[-1]
     out = np.empty_like(x)
     mask = np.empty(x.shape, np.uint8)
-    lib().tfo_softmax_dropout_exact(_p(x), _p(out), _p(mask), x.size // L, L,
-                                    1 if x.dtype == np.float16 else 0, p, seed, first_row,
-                                    vec, warps, threads)
+    fn = lib().tfo_softmax_dropout_exact_online if online else lib().tfo_softmax_dropout_exact
+    fn(_p(x), _p(out), _p(mask), x.size // L, L, 1 if x.dtype == np.float16 else 0, p, seed, first_row,
+       vec, warps, threads)
     return out, mask
 
 

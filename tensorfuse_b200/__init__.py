@@ -188,11 +188,47 @@ def softmax_schedule(row_len: int, dtype=np.float16, aligned16: bool = True):
     return v.value, w.value
 
 
+def softmax_schedule_ex(row_len: int, dtype=np.float16, aligned16: bool = True):
+    """(vec, warps, online): softmax_schedule plus whether the row is summed online."""
+    v, w, o = C.c_int(), C.c_int(), C.c_int()
+    _L.tensorfuse_b200_softmax_schedule_ex(int(row_len), int(_NP_TO_DT[np.dtype(dtype)]), int(aligned16),
+                                           C.byref(v), C.byref(w), C.byref(o))
+    return v.value, w.value, o.value
+
+
 def plan_shards(rows: int, parts: int, align: int = 1):
     b = (C.c_longlong * parts)()
     c = (C.c_longlong * parts)()
     _L.tensorfuse_b200_plan_shards(rows, parts, align, b, c)
     return list(b), list(c)
+
+
+# ------------------------------------------------------- immutable weights
+def _ptr_and_bytes(x):
+    if _is_torch(x):
+        return int(x.data_ptr()), int(x.numel() * x.element_size())
+    a = np.asarray(x)
+    return int(a.ctypes.data), int(a.nbytes)
+
+
+def register_weights(*tensors):
+    """Declare weight buffers (numpy arrays in host memory or torch CUDA tensors)
+    immutable: the host-buffer GEMM then keeps one device copy per GPU instead of
+    uploading them on every call, and ``fused_transformer_layer`` builds its
+    fused query/key/value weight once.  Call ``invalidate_weights`` before
+    changing or freeing them."""
+    for t in tensors:
+        ptr, nbytes = _ptr_and_bytes(t)
+        st = _auto_init(_L.tensorfuse_b200_register_weights, ptr, nbytes)
+        _check("register_weights", st)
+
+
+def invalidate_weights(*tensors):
+    """Forget registered weight buffers (all of them when called without arguments)."""
+    if not tensors:
+        _check("invalidate_weights", _L.tensorfuse_b200_invalidate_weights(None))
+    for t in tensors:
+        _check("invalidate_weights", _L.tensorfuse_b200_invalidate_weights(_ptr_and_bytes(t)[0]))
 
 
 # ------------------------------------------------------------ pinned memory
@@ -664,6 +700,6 @@ def is_gpu_supported() -> bool:
 __all__ = ["Status", "DataType", "Config", "TensorFuseStatus", "TensorFuseDataType",
            "TensorFuseConfig", "init", "shutdown", "cleanup", "get_version", "get_error_string",
            "fused_gemm_bias_gelu", "fused_softmax_dropout", "fused_softmax_dropout_masked", "fused_multi_head_attention", "fused_transformer_layer", "add_layernorm", "quantize_int8",
-           "set_random_seed", "device_ids", "watchdog_status", "launch_count", "softmax_schedule",
-           "plan_shards", "pinned_empty", "is_gpu_supported", "INT8_DEQUANT", "INT8_LEGACY",
+           "set_random_seed", "device_ids", "watchdog_status", "launch_count", "softmax_schedule", "softmax_schedule_ex",
+           "plan_shards", "pinned_empty", "register_weights", "invalidate_weights", "is_gpu_supported", "INT8_DEQUANT", "INT8_LEGACY",
            "INT8_RAW", "TENSORFUSE_MAX_DIMS"]

@@ -97,6 +97,7 @@ def _load():
     sig("tensorfuse_b200_attention", i, [vp, vp, vp, vp, i, i, i, i, i] + [ll] * 12 + [i, f, f, ull, vp, st])
     sig("tensorfuse_b200_softmax_dropout_rows", i, [vp, vp, vp, ll, i, i, f, ull, ull, st])
     sig("tensorfuse_b200_softmax_schedule", None, [i, i, i, C.POINTER(i), C.POINTER(i)])
+    sig("tensorfuse_b200_softmax_schedule_ex", None, [i, i, i, C.POINTER(i), C.POINTER(i), C.POINTER(i)])
     sig("tensorfuse_b200_set_random_seed", None, [ull])
     sig("tensorfuse_b200_last_softmax_seed", ull, [])
     sig("tensorfuse_b200_gemm_bias_gelu_host", i, [vp, vp, vp, vp, i, i, i, i, i, i, i, f, f])

@@ -482,13 +482,22 @@ def _from_c(ct: _lib.Tensor) -> Tensor:
     return t
 
 
+def _allocate(cs: _lib.Shape, dtype, device_id, prefix: str) -> Tensor:
+    """tensorfuse_allocate_tensor; the library is initialised with its defaults
+    first if it is not yet (the binding's from_numpy needs no initialisation --
+    it only wraps the host pointer -- and callers rely on that)."""
+    ct = _lib.Tensor()
+    st = _L.tensorfuse_allocate_tensor(C.byref(ct), C.byref(cs), int(dtype), int(device_id))
+    if st == Status.NOT_INITIALIZED:
+        init()
+        st = _L.tensorfuse_allocate_tensor(C.byref(ct), C.byref(cs), int(dtype), int(device_id))
+    _raise_unless_ok(prefix, st)
+    return _from_c(ct)
+
+
 def allocate_tensor(shape, dtype, device_id=0):
     """memory_bindings.cpp:23-32 -> tensorfuse_allocate_tensor."""
-    ct = _lib.Tensor()
-    cs = _as_shape(shape)._to_c()
-    st = _L.tensorfuse_allocate_tensor(C.byref(ct), C.byref(cs), int(dtype), int(device_id))
-    _raise_unless_ok("Failed to allocate tensor: ", st)
-    return _from_c(ct)
+    return _allocate(_as_shape(shape)._to_c(), dtype, device_id, "Failed to allocate tensor: ")
 
 
 def free_tensor(tensor):
@@ -535,11 +544,7 @@ def create_tensor(shape, dtype, device_id=0):
     """tensor_bindings.cpp:58-71."""
     if any(int(d) < 0 for d in shape):
         raise RuntimeError("Failed to create tensor: " + _err(Status.INVALID_TENSOR_SHAPE))
-    ct = _lib.Tensor()
-    cs = Shape(list(shape))._to_c()
-    st = _L.tensorfuse_allocate_tensor(C.byref(ct), C.byref(cs), int(dtype), int(device_id))
-    _raise_unless_ok("Failed to create tensor: ", st)
-    return _from_c(ct)
+    return _allocate(Shape(list(shape))._to_c(), dtype, device_id, "Failed to create tensor: ")
 
 
 def from_numpy(array, device_id=0):

@@ -78,6 +78,15 @@ def layer_params(p: dict, cfg: EncoderConfig) -> dict:
     return p["_params"]
 
 
+def register_layer_weights(layers, cfg: EncoderConfig):
+    """Registers the query/key/value projections of every layer as immutable, so
+    that tensorfuse_fused_transformer_layer concatenates them once instead of on
+    every call.  Undo with ``tf.invalidate_weights()`` before the weights change."""
+    for p in layers:
+        lp = layer_params(p, cfg)
+        tf.register_weights(lp["query_weight"], lp["key_weight"], lp["value_weight"])
+
+
 def layer_seed(seed: int, layer: int) -> int:
     return (seed * 1000003 + layer * 131) & 0xFFFFFFFFFFFF
 

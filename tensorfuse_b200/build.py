@@ -23,7 +23,7 @@ LIB = os.path.join(LIBDIR, "libtensorfuse.so")
 
 SOURCES = ["softmax_dropout.cu", "gemm_simt.cu", "gemm_tc.cu", "attention.cu", "quantize.cu", "layernorm.cu", "transformer_layer.cpp", "runtime.cpp", "c_api.cpp",
            "host_ops.cpp", "noalloc.cu", "profiler.cpp", "cxx_api.cpp"]
-HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh", "gemm_tc_pair_kernel.cuh", "attention_tc_kernel.cuh", "philox.cuh", "tma_host.h"]
+HEADERS = ["kernels.h", "ptx.cuh", "epilogue.cuh", "runtime.h", "gemm_tc_kernel.cuh", "gemm_tc_pair_kernel.cuh", "gemm_tf32x3_kernel.cuh", "attention_tc_kernel.cuh", "philox.cuh", "tma_host.h"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC,-fvisibility=default", "-DTENSORFUSE_WITH_CUDA_RUNTIME",

@@ -540,6 +540,13 @@ void tensorfuse_b200_softmax_schedule(int row_len, int dtype, int aligned16, int
   if (warps) *warps = s.warps;
 }
 
+void tensorfuse_b200_softmax_schedule_ex(int row_len, int dtype, int aligned16, int* vec, int* warps, int* online) {
+  const SoftmaxSchedule s = softmax_schedule(row_len, dtype, aligned16 != 0);
+  if (vec) *vec = s.vec;
+  if (warps) *warps = s.warps;
+  if (online) *online = s.online;
+}
+
 void tensorfuse_b200_set_random_seed(unsigned long long seed) { Runtime::get().set_seed(seed); }
 unsigned long long tensorfuse_b200_last_softmax_seed(void) { return t_last_seed; }
 

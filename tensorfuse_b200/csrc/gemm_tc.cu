@@ -17,6 +17,8 @@
 
 #include "gemm_tc_kernel.cuh"
 #include "gemm_tc_pair_kernel.cuh"
+#include "gemm_tf32x3_kernel.cuh"
+#include "runtime.h"
 #include "tma_host.h"
 
 namespace tfb {
@@ -183,6 +185,100 @@ bool use_pair_form(const GemmArgs& a) {
   return a.M > tc::TBM;
 }
 
+// FP32 on the tensor cores: split A and B into TF32 hi/lo planes (stream-ordered
+// scratch from the library's workspace pool), then the three-product kernel.
+template <int EPI>
+LaunchResult run_tf32x3(const GemmArgs& a, cudaStream_t stream) {
+  using namespace tf32x3;
+  auto kernel = gemm_tf32x3_kernel<EPI>;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return kCudaError;
+  static bool ready[64] = {};
+  static int max_clusters[64] = {};
+  static std::mutex mu;
+  {
+    std::lock_guard<std::mutex> g(mu);
+    if (!ready[dev]) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, X_SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return kCudaError;
+      }
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * (unsigned)(sm_count(dev) / 2));
+      cfg.blockDim = dim3(NUM_THREADS);
+      cfg.dynamicSmemBytes = X_SMEM_BYTES;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr; cfg.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = 0; }
+      max_clusters[dev] = n;
+      ready[dev] = true;
+    }
+  }
+  if (max_clusters[dev] <= 0) return kLaunchFailed;      // cannot co-schedule CTA pairs here
+  cudaMemPool_t pool = Runtime::get().workspace_pool(dev);
+  if (pool == nullptr) return kLaunchFailed;
+  const size_t a_elems = (size_t)a.M * a.K, b_elems = (size_t)a.K * a.N;
+  auto round_up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t a_bytes = round_up(a_elems * 4), b_bytes = round_up(b_elems * 4);
+  char* ws = nullptr;
+  if (cudaMallocFromPoolAsync(reinterpret_cast<void**>(&ws), 2 * a_bytes + 2 * b_bytes, pool, stream) != cudaSuccess) {
+    cudaGetLastError();
+    return kLaunchFailed;
+  }
+  float* ah = reinterpret_cast<float*>(ws);
+  float* al = reinterpret_cast<float*>(ws + a_bytes);
+  float* bh = reinterpret_cast<float*>(ws + 2 * a_bytes);
+  float* bl = reinterpret_cast<float*>(ws + 2 * a_bytes + b_bytes);
+  const int sms = sm_count(dev);
+  auto split = [&](const void* x, float* hi, float* lo, size_t elems) {
+    const long long n4 = (long long)(elems / 4);
+    const long long want = (n4 + 255) / 256;
+    const int grid = (int)(want < (long long)sms * 8 ? want : (long long)sms * 8);
+    split_tf32_kernel<<<grid > 0 ? grid : 1, 256, 0, stream>>>(static_cast<const float4*>(x), reinterpret_cast<float4*>(hi),
+                                                             reinterpret_cast<float4*>(lo), n4);
+  };
+  split(a.A, ah, al, a_elems);
+  {
+    const long long tiles = (long long)((a.N + 31) / 32) * ((a.K + 31) / 32);
+    const int grid = (int)(tiles < (long long)sms * 8 ? tiles : (long long)sms * 8);
+    split_transpose_tf32_kernel<<<grid, dim3(32, 8), 0, stream>>>(static_cast<const float*>(a.B), bh, bl, a.K, a.N);
+  }
+  count_launch(2);
+  LaunchResult res = kOk;
+  CUtensorMap mah, mal, mbh, mbl, mc;
+  if (!cached_map(MapKey{ah, 4, a.M, a.K, TBM}, &mah) || !cached_map(MapKey{al, 4, a.M, a.K, TBM}, &mal) ||
+      !cached_map(MapKey{bh, 4, a.N, a.K, 128}, &mbh) || !cached_map(MapKey{bl, 4, a.N, a.K, 128}, &mbl) ||
+      !cached_map(MapKey{a.C, 4, a.M, a.N, 32}, &mc)) {
+    res = kLaunchFailed;
+  } else {
+    const int tiles = ((a.M + 2 * TBM - 1) / (2 * TBM)) * ((a.N + TBN - 1) / TBN);
+    const int pairs = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
+    EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev, nullptr};
+    kernel<<<2 * pairs, NUM_THREADS, X_SMEM_BYTES, stream>>>(mah, mal, mbh, mbl, mc, a.bias, a.bias_dtype, a.M, a.N, a.K,
+                                                            ep, watchdog_word());
+    count_launch();
+    if (cudaGetLastError() != cudaSuccess) res = kLaunchFailed;
+  }
+  cudaFreeAsync(ws, stream);
+  return res;
+}
+
+// 0 = by size, 1 = CUDA cores only, 2 = tensor cores wherever eligible
+// (TENSORFUSE_B200_FP32_FORM = simt | tf32x3, read once; for measurements and tests).
+int fp32_form_override() {
+  static const int mode = [] {
+    const char* e = std::getenv("TENSORFUSE_B200_FP32_FORM");
+    if (e && std::strcmp(e, "simt") == 0) return 1;
+    if (e && std::strcmp(e, "tf32x3") == 0) return 2;
+    return 0;
+  }();
+  return mode;
+}
+
 template <int KIND, int EPI, typename TOut>
 LaunchResult run_any(const GemmArgs& a, cudaStream_t stream) {
   if (use_pair_form(a)) {
@@ -227,10 +323,28 @@ LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream) {
   return run_any<1, kEpiI8Raw, int>(a, stream);
 }
 
+bool gemm_tf32x3_eligible(const GemmArgs& a) {
+  if (a.in_dtype != kF32 || a.out_dtype != kF32) return false;
+  if (a.epilogue != kEpiGelu && a.epilogue != kEpiLinear) return false;
+  if (a.M <= 0 || a.N <= 0 || a.K <= 0 || !a.bias) return false;
+  if (((uintptr_t)a.A | (uintptr_t)a.B | (uintptr_t)a.C) & 15u) return false;
+  if (a.K % 4 != 0 || a.N % 4 != 0) return false;                  // 16-byte row pitches for the tensor maps
+  const int mode = fp32_form_override();
+  if (mode == 1) return false;
+  if (mode == 2) return true;
+  // small problems stay on the CUDA-core kernel: the split pass and a cluster launch cost more than they save
+  return (double)a.M * a.N * a.K >= 16777216.0;
+}
+
 LaunchResult launch_gemm(const GemmArgs& a, cudaStream_t stream) {
   // the epilogues read the bias as FP32, FP16 or BF16 and nothing else
   if (a.epilogue != kEpiI8Raw && a.bias_dtype != kF32 && a.bias_dtype != kF16 && a.bias_dtype != kBF16)
     return kUnsupported;
+  if (gemm_tf32x3_eligible(a)) {
+    const LaunchResult r = a.epilogue == kEpiGelu ? run_tf32x3<kEpiGelu>(a, stream) : run_tf32x3<kEpiLinear>(a, stream);
+    if (r != kLaunchFailed) return r;
+    cudaGetLastError();     // no CTA pairs / no workspace: the CUDA-core kernel still runs
+  }
   if (gemm_tc_eligible(a)) return launch_gemm_tc(a, stream);
   return launch_gemm_simt(a, stream);
 }

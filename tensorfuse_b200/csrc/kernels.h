@@ -21,11 +21,14 @@ enum LaunchResult : int {
 // ------------------------------------------------------- softmax + dropout
 // Summation schedule the kernel uses for a row of L elements; the CPU oracle
 // takes the same two numbers to reproduce the result bit for bit.
-//   vec   : consecutive elements owned by one thread per step (8 or 1)
-//   warps : warps cooperating on one row (1 = warp-per-row kernel)
+//   vec    : consecutive elements owned by one thread per step (8 or 1)
+//   warps  : warps cooperating on one row (1 = warp-per-row kernel)
+//   online : 1 when the row is too long for shared memory and the sum is formed
+//            in one sweep with a running maximum (rescaled partial sums)
 struct SoftmaxSchedule {
   int vec;
   int warps;
+  int online;
 };
 SoftmaxSchedule softmax_schedule(int L, int dtype, bool aligned16);
 
@@ -74,6 +77,10 @@ struct GemmArgs {
 // FP16, BF16, INT8 or FP8-E4M3 operands, 16-byte aligned base pointers and row pitches.
 bool gemm_tc_eligible(const GemmArgs& a);
 LaunchResult launch_gemm_tc(const GemmArgs& a, cudaStream_t stream);
+// FP32 operands on the tensor cores (three TF32 products per FP32 product, FP32
+// accumulation): 16-byte aligned pointers, K and N multiples of 4, problems of at
+// least 2^24 multiply-adds.  Uses stream-ordered scratch for the split operands.
+bool gemm_tf32x3_eligible(const GemmArgs& a);
 // Any shape, any alignment; CUDA-core FMA kernel with the same fused epilogue.
 LaunchResult launch_gemm_simt(const GemmArgs& a, cudaStream_t stream);
 // Picks the tensor-core kernel when eligible, else the CUDA-core kernel.

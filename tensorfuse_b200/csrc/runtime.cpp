@@ -120,6 +120,7 @@ TensorFuseStatus Runtime::shutdown() {
   }
   ctxs_.clear();
   static_weights_.clear();
+  drop_fused_qkv_locked(nullptr);
   for (auto& kv : pools_) {
     DeviceGuard dg(kv.first);
     cudaDeviceSynchronize();           // stream-ordered frees into the pool have completed
@@ -167,6 +168,30 @@ cudaMemPool_t Runtime::workspace_pool(int device) {
   return pool;
 }
 
+Runtime::FusedQkv* Runtime::fused_qkv_slot(int device, const void* wq, const void* wk, const void* wv, bool* fresh) {
+  std::lock_guard<std::mutex> g(mu_);
+  if (!static_weights_.count(wq) || !static_weights_.count(wk) || !static_weights_.count(wv)) return nullptr;
+  const QkvKey key{device, wq, wk, wv};
+  auto it = fused_qkv_.find(key);
+  *fresh = it == fused_qkv_.end();
+  return &fused_qkv_[key];
+}
+
+void Runtime::drop_fused_qkv_locked(const void* ptr) {
+  for (auto it = fused_qkv_.begin(); it != fused_qkv_.end();) {
+    if (ptr == nullptr || it->first.q == ptr || it->first.k == ptr || it->first.v == ptr) {
+      DeviceGuard dg(it->first.dev);
+      cudaDeviceSynchronize();          // a layer that reads the copy may still be running
+      if (it->second.w) cudaFree(it->second.w);
+      if (it->second.b) cudaFree(it->second.b);
+      it = fused_qkv_.erase(it);
+    } else {
+      ++it;
+    }
+  }
+  cudaGetLastError();
+}
+
 void Runtime::register_weights(const void* host_ptr, size_t bytes) {
   std::lock_guard<std::mutex> g(mu_);
   if (host_ptr && bytes) static_weights_[host_ptr] = bytes;
@@ -182,6 +207,7 @@ void Runtime::invalidate_weights(const void* host_ptr) {
     std::lock_guard<std::mutex> g(mu_);
     if (host_ptr) static_weights_.erase(host_ptr);
     else static_weights_.clear();
+    drop_fused_qkv_locked(host_ptr);
     for (auto& c : ctxs_) ctxs.push_back(c.get());
   }
   for (DeviceCtx* c : ctxs) {

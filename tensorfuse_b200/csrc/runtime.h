@@ -56,6 +56,11 @@ class Runtime {
 
   // Host ranges the caller has declared immutable: the host-buffer operators
   // keep one device copy per selected device instead of uploading per call.
+  // Concatenated copy of three registered device weight matrices (and biases),
+  // kept per device until the registration of any of them is invalidated.
+  // Returns null when it has to be (re)built: the caller fills `*slot` then.
+  struct FusedQkv { void* w = nullptr; void* b = nullptr; size_t w_bytes = 0, b_bytes = 0; };
+  FusedQkv* fused_qkv_slot(int device, const void* wq, const void* wk, const void* wv, bool* fresh);
   void register_weights(const void* host_ptr, size_t bytes);
   void invalidate_weights(const void* host_ptr);   // null: all of them
   size_t registered_bytes(const void* host_ptr);   // 0 when not registered
@@ -77,6 +82,17 @@ class Runtime {
   std::vector<std::unique_ptr<DeviceCtx>> ctxs_;
   std::map<const void*, size_t> static_weights_;   // registered host ranges: address -> bytes
   std::map<int, cudaMemPool_t> pools_;
+  struct QkvKey {
+    int dev; const void* q; const void* k; const void* v;
+    bool operator<(const QkvKey& o) const {
+      if (dev != o.dev) return dev < o.dev;
+      if (q != o.q) return q < o.q;
+      if (k != o.k) return k < o.k;
+      return v < o.v;
+    }
+  };
+  std::map<QkvKey, FusedQkv> fused_qkv_;
+  void drop_fused_qkv_locked(const void* ptr);   // entries that involve ptr (null: all)
   bool seeded_ = false;
   unsigned long long seed_base_ = 0, seed_calls_ = 0;
 };

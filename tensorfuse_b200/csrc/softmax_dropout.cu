@@ -30,6 +30,8 @@
 // reproduces the same mask.
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "kernels.h"
 #include "philox.cuh"
@@ -298,13 +300,105 @@ __device__ __forceinline__ uint32_t hmax2_bits(uint32_t a, uint32_t b) {
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
+// Dropout decisions of one lane's units of one row.  They depend on positions
+// only; up to four Philox blocks are generated with interleaved rounds.
+template <int CH, bool DROP>
+__device__ __forceinline__ void row_keep_masks(const SmParams& p, long long row, int lane, uint32_t (&km)[CH][4]) {
+  const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)p.L) >> 3;
+  constexpr int NB = CH < 4 ? CH : 4;
+#pragma unroll
+  for (int c0 = 0; c0 < CH; c0 += NB) {
+    if (DROP) {
+      unsigned long long blk[NB];
+      uint32_t o[NB][4];
+#pragma unroll
+      for (int q = 0; q < NB; ++q) blk[q] = blk0 + (unsigned)(lane + 32 * (c0 + q));
+      philox_blocks<NB>(blk, p.key, o);
+#pragma unroll
+      for (int q = 0; q < NB; ++q) masks_from_words<true>(p, o[q], km[c0 + q]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < NB; ++q) masks_from_words<false>(p, km[c0 + q], km[c0 + q]);
+    }
+  }
+}
+
+// One row held by a warp as CH units per lane (unit c of lane l = elements
+// (l + 32c)*8 ..): maximum, exponentials e2[c][k] (elements 2k, 2k+1 of unit c)
+// and the factor g = keep_scale / sum.  FP16 storage keeps the row packed for
+// as long as possible: the maximum and the clamp at lo are taken on half2 words,
+// the widening to FP32 happens once.  The order of every operation is fixed
+// (it is the order the CPU restatement follows).
+template <typename T, int CH, bool EXT>
+__device__ __forceinline__ uint64_t row_exponentials(const SmParams& p, const Unit<T> (&cur)[CH], long long row,
+                                                     int lane, uint64_t (&e2)[CH][4]) {
+  constexpr bool HF = sizeof(T) == 2 && !EXT;
+  const int len = valid_length<EXT>(p, row);
+  float m;
+  if constexpr (HF) {
+    uint32_t m2 = 0xFC00FC00u;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const uint4 r = cur[c].raw;
+      m2 = hmax2_bits(hmax2_bits(m2, hmax2_bits(r.x, r.y)), hmax2_bits(r.z, r.w));
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) m2 = hmax2_bits(m2, __shfl_xor_sync(0xffffffffu, m2, off));
+    const float2 mf = __half22float2(*reinterpret_cast<const __half2*>(&m2));
+    m = fmaxf(mf.x, mf.y);
+  } else {
+    m = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      float x[8];
+      cur[c].widen(x);
+      adjust8<EXT>(x, (lane + 32 * c) * 8, len, p.scale);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
+    }
+    m = warp_max(m);
+  }
+  const bool all_masked = m == -INFINITY;   // defined as an all-zero output row
+  if (all_masked) m = 0.0f;
+  const ExpCtx ctx = make_exp_ctx<HF>(m);
+
+  uint64_t s2 = pack2(0.0f, 0.0f);
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    if constexpr (HF) {
+      const __half lo_h = __float2half_rn(ctx.lo);
+      const __half2 lo2 = __halves2half2(lo_h, lo_h);
+      const uint32_t lo_bits = *reinterpret_cast<const uint32_t*>(&lo2);
+      const uint32_t w[4] = {cur[c].raw.x, cur[c].raw.y, cur[c].raw.z, cur[c].raw.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t xw = hmax2_bits(w[k], lo_bits);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw));
+        e2[c][k] = exp_pair<true, true>(f.x, f.y, ctx);
+        s2 = add2(s2, e2[c][k]);
+      }
+    } else {
+      float x[8];
+      cur[c].widen(x);
+      adjust8<EXT>(x, (lane + 32 * c) * 8, len, p.scale);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        e2[c][k] = exp_pair<false>(x[2 * k], x[2 * k + 1], ctx);
+        s2 = add2(s2, e2[c][k]);
+      }
+    }
+  }
+  const float2 s = unpack2(s2);
+  const float total = warp_sum_butterfly(__fadd_rn(s.x, s.y));
+  const float inv = (total == 0.0f || all_masked) ? 0.0f : __fdiv_rn(1.0f, total);
+  const float g = __fmul_rn(inv, p.keep_scale);
+  return pack2(g, g);
+}
+
 // CH = units per lane (row length <= 256*CH).  8 warps per CTA, grid-stride
 // over rows, next row's loads in flight while the current row is processed.
-// FP16 storage keeps the row packed for as long as possible: the maximum and
-// the clamp at lo are taken on half2 words, the widening to FP32 happens once.
 template <typename T, int CH, bool DROP, bool EXT>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
-  constexpr bool HF = sizeof(T) == 2 && !EXT;
   const int lane = threadIdx.x & 31;
   const int L = p.L;
   const long long stride = (long long)gridDim.x * 8;
@@ -331,92 +425,12 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
       if (valid[c] && next_row < p.rows) nxt[c].load(in + next_row * L + (lane + 32 * c) * 8);
       else nxt[c].fill_neg_inf();
     }
-
-    // Dropout decisions of this lane's units.  They depend on positions only, so they are
-    // generated here, up to four Philox blocks with interleaved rounds, where their integer
-    // work overlaps the latency of the loads above and the reductions below.
+    // generated here, where the integer work overlaps the latency of the loads
+    // above and of the reductions below
     uint32_t km[CH][4];
-    {
-      const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)L) >> 3;
-      constexpr int NB = CH < 4 ? CH : 4;
-#pragma unroll
-      for (int c0 = 0; c0 < CH; c0 += NB) {
-        if (DROP) {
-          unsigned long long blk[NB];
-          uint32_t o[NB][4];
-#pragma unroll
-          for (int q = 0; q < NB; ++q) blk[q] = blk0 + (unsigned)(lane + 32 * (c0 + q));
-          philox_blocks<NB>(blk, p.key, o);
-#pragma unroll
-          for (int q = 0; q < NB; ++q) masks_from_words<true>(p, o[q], km[c0 + q]);
-        } else {
-#pragma unroll
-          for (int q = 0; q < NB; ++q) masks_from_words<false>(p, km[c0 + q], km[c0 + q]);
-        }
-      }
-    }
-    const int len = valid_length<EXT>(p, row);
-    float m;
-    if constexpr (HF) {
-      uint32_t m2 = 0xFC00FC00u;
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        const uint4 r = cur[c].raw;
-        m2 = hmax2_bits(hmax2_bits(m2, hmax2_bits(r.x, r.y)), hmax2_bits(r.z, r.w));
-      }
-#pragma unroll
-      for (int off = 16; off >= 1; off >>= 1) m2 = hmax2_bits(m2, __shfl_xor_sync(0xffffffffu, m2, off));
-      const float2 mf = __half22float2(*reinterpret_cast<const __half2*>(&m2));
-      m = fmaxf(mf.x, mf.y);
-    } else {
-      m = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < CH; ++c) {
-        float x[8];
-        cur[c].widen(x);
-        adjust8<EXT>(x, (lane + 32 * c) * 8, len, p.scale);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
-      }
-      m = warp_max(m);
-    }
-    const bool all_masked = m == -INFINITY;   // defined as an all-zero output row
-    if (all_masked) m = 0.0f;
-    const ExpCtx ctx = make_exp_ctx<HF>(m);
-
+    row_keep_masks<CH, DROP>(p, row, lane, km);
     uint64_t e2[CH][4];
-    uint64_t s2 = pack2(0.0f, 0.0f);
-#pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      if constexpr (HF) {
-        const __half lo_h = __float2half_rn(ctx.lo);
-        const __half2 lo2 = __halves2half2(lo_h, lo_h);
-        const uint32_t lo_bits = *reinterpret_cast<const uint32_t*>(&lo2);
-        const uint32_t w[4] = {cur[c].raw.x, cur[c].raw.y, cur[c].raw.z, cur[c].raw.w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint32_t xw = hmax2_bits(w[k], lo_bits);
-          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw));
-          e2[c][k] = exp_pair<true, true>(f.x, f.y, ctx);
-          s2 = add2(s2, e2[c][k]);
-        }
-      } else {
-        float x[8];
-        cur[c].widen(x);
-        adjust8<EXT>(x, (lane + 32 * c) * 8, len, p.scale);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          e2[c][k] = exp_pair<false>(x[2 * k], x[2 * k + 1], ctx);
-          s2 = add2(s2, e2[c][k]);
-        }
-      }
-    }
-    const float2 s = unpack2(s2);
-    const float total = warp_sum_butterfly(__fadd_rn(s.x, s.y));
-    const float inv = (total == 0.0f || all_masked) ? 0.0f : __fdiv_rn(1.0f, total);
-    const float g = __fmul_rn(inv, p.keep_scale);
-    const uint64_t g2 = pack2(g, g);
-
+    const uint64_t g2 = row_exponentials<T, CH, EXT>(p, cur, row, lane, e2);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       if (valid[c]) {
@@ -428,6 +442,297 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
     for (int c = 0; c < CH; ++c) cur[c] = nxt[c];
   }
 }
+
+// ----------------------------------------------------- streaming (bulk-copy) kernel
+// The same per-row arithmetic, fed by the copy engine instead of by the warps'
+// own loads.  Rows are dense, so a tile of R consecutive rows is one contiguous
+// byte range:
+//   * a producer warp streams tiles into a ring of shared-memory stages with
+//     cp.async.bulk (completion counted in bytes on an mbarrier);
+//   * eight consumer warps take RPW rows each out of a stage, release it as soon
+//     as the rows are in registers, and write their results into their own
+//     double-buffered staging area, which leaves through cp.async.bulk stores;
+//   * with dropout, four more warps do nothing but generate the keep decisions:
+//     the Philox blocks of a tile are consecutive counters, so these warps fill
+//     the tile's mask bytes (one 8-byte store per block) into one of two mask
+//     buffers, from which one bulk store writes the mask to memory and the
+//     consumers read their keep bits.  The integer work of the generator thus
+//     runs in issue slots the consumers leave free, instead of in front of
+//     every row's arithmetic.  Without dropout the consumers write the (all
+//     ones) mask bytes themselves.
+// The warps never wait on global memory: several tiles per SM are in flight in
+// each direction, whatever the arithmetic is doing.
+namespace stream {
+
+constexpr int WARPS = 8;            // consumer warps; warp WARPS is the producer
+constexpr int RNG_WARPS = 4;        // warps WARPS+1 .. : dropout decisions (kernels with dropout only)
+constexpr int STAGES = 3;
+constexpr int MASK_BUFS = 2;        // tile-sized mask buffers filled by the generator warps
+template <bool DROP> struct Threads { static constexpr int value = (WARPS + 1 + (DROP ? RNG_WARPS : 0)) * 32; };
+enum : int { kWdStreamFull = 301, kWdStreamEmpty = 302, kWdMaskFull = 303, kWdMaskEmpty = 304 };
+__device__ __forceinline__ void rng_warps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(RNG_WARPS * 32) : "memory"); }
+__device__ __forceinline__ uint2 lds8(uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+
+template <typename T, int CH> struct Cfg {
+  static constexpr int ROW_BYTES_MAX = CH * 256 * (int)sizeof(T);
+  // rows per consumer warp and tile: tiles of about 16 KB of input
+  static constexpr int RPW = ROW_BYTES_MAX <= 512 ? 4 : ROW_BYTES_MAX <= 1024 ? 2 : 1;
+  static constexpr int R = WARPS * RPW;
+};
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               ::"l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_le1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ uint4 lds16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts16(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts8(uint32_t addr, uint2 v) {
+  asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(v.x), "r"(v.y) : "memory");
+}
+
+template <typename T> __device__ __forceinline__ void unit_from_smem(Unit<T>& u, uint32_t addr);
+template <> __device__ __forceinline__ void unit_from_smem<__half>(Unit<__half>& u, uint32_t addr) { u.raw = lds16(addr); }
+template <> __device__ __forceinline__ void unit_from_smem<float>(Unit<float>& u, uint32_t addr) {
+  u.raw[0] = lds16(addr);
+  u.raw[1] = lds16(addr + 16);
+}
+
+// finish_unit_masked with shared-memory destinations; WRITE_MASK = false when
+// the mask bytes are already where they belong (written by the generator warps)
+template <typename T, bool WRITE_MASK>
+__device__ __forceinline__ void finish_unit_smem(const uint64_t (&e2)[4], uint64_t g2, uint32_t out_addr,
+                                                 uint32_t mask_addr, const uint32_t (&km)[4]) {
+  if constexpr (WRITE_MASK) {
+    uint2 mb;
+    mb.x = __byte_perm(km[0], km[1], 0x6420) & 0x01010101u;
+    mb.y = __byte_perm(km[2], km[3], 0x6420) & 0x01010101u;
+    sts8(mask_addr, mb);
+  }
+  float2 y[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) y[k] = unpack2(mul2(e2[k], g2));
+  if constexpr (sizeof(T) == 2) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const __half2 h = __floats2half2_rn(y[k].x, y[k].y);
+      w[k] = *reinterpret_cast<const uint32_t*>(&h) & km[k];
+    }
+    sts16(out_addr, make_uint4(w[0], w[1], w[2], w[3]));
+  } else {
+    uint32_t v[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      v[2 * k] = (km[k] & 0xFFFFu) ? __float_as_uint(y[k].x) : 0u;
+      v[2 * k + 1] = (km[k] >> 16) ? __float_as_uint(y[k].y) : 0u;
+    }
+    sts16(out_addr, make_uint4(v[0], v[1], v[2], v[3]));
+    sts16(out_addr + 16, make_uint4(v[4], v[5], v[6], v[7]));
+  }
+}
+
+// Eight mask bytes (0 / 1) of one Philox block -> the four mask words of finish_unit_*.
+__device__ __forceinline__ void masks_from_bytes(uint2 mb, uint32_t (&km)[4]) {
+  const uint32_t t0 = mb.x * 0xFFu, t1 = mb.y * 0xFFu;     // bytes 0x00 / 0xFF
+  km[0] = __byte_perm(t0, 0u, 0x1100);
+  km[1] = __byte_perm(t0, 0u, 0x3322);
+  km[2] = __byte_perm(t1, 0u, 0x1100);
+  km[3] = __byte_perm(t1, 0u, 0x3322);
+}
+
+// dynamic shared memory:
+//   [STAGES x tile_bytes | WARPS x 2 x staging | DROP: MASK_BUFS x R*L mask bytes | barriers | abort flag]
+// staging of one consumer warp: RPW rows of output (+ RPW*L mask bytes without dropout)
+template <typename T, int CH, bool DROP, bool EXT>
+__global__ void __launch_bounds__(Threads<DROP>::value) softmax_stream_kernel(const SmParams p, int* status) {
+  using C = Cfg<T, CH>;
+  constexpr int RPW = C::RPW, R = C::R;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int L = p.L;
+  const uint32_t row_bytes = (uint32_t)L * (uint32_t)sizeof(T);
+  const uint32_t tile_bytes = R * row_bytes;
+  const uint32_t tile_mask_bytes = R * (uint32_t)L;
+  const uint32_t wout_bytes = RPW * row_bytes, wmask_bytes = DROP ? 0u : RPW * (uint32_t)L;
+  const uint32_t wbuf_bytes = wout_bytes + wmask_bytes;            // one staging buffer of one warp
+  const uint32_t s_in = smem_u32(smem);
+  const uint32_t s_out = s_in + STAGES * tile_bytes;
+  const uint32_t s_mask = s_out + WARPS * 2 * wbuf_bytes;
+  const uint32_t bars = s_mask + (DROP ? MASK_BUFS * tile_mask_bytes : 0u);   // every size is a multiple of 16
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto mfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
+  auto mempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + MASK_BUFS + b); };
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bars - s_in) + 8 * (2 * STAGES + 2 * MASK_BUFS));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long num_tiles = (p.rows + R - 1) / R;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), WARPS); }
+    for (int b = 0; b < MASK_BUFS; ++b) { mbar_init(mfull_bar(b), 1); mbar_init(mempty_bar(b), WARPS); }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == WARPS) {
+    // ---------------------------------------------------------------- producer
+    if (elect_one()) {
+      const char* in = static_cast<const char*>(p.in);
+      uint32_t stage = 0, phase = 0;
+      for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, status, kWdStreamEmpty)) break;
+        const long long row0 = tile * R;
+        const long long nrows = min((long long)R, p.rows - row0);
+        const uint32_t bytes = (uint32_t)nrows * row_bytes;
+        mbar_arrive_expect_tx(full_bar(stage), bytes);
+        bulk_load(s_in + stage * tile_bytes, in + row0 * (long long)row_bytes, bytes, full_bar(stage));
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp > WARPS) {
+    // ------------------------------------------------- dropout decision generator
+    if constexpr (DROP) {
+      const int rt = threadIdx.x - (WARPS + 1) * 32;            // 0 .. RNG_WARPS*32-1
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+        const uint32_t b = it % MASK_BUFS, parity = (it / MASK_BUFS) & 1u;
+        // the consumers have read the previous contents, and the copy engine has read them too
+        if (ok && !mbar_wait(mempty_bar(b), parity ^ 1u, abort_flag, status, kWdMaskEmpty)) ok = false;
+        if (rt == 0) bulk_wait_read_le1();
+        rng_warps_sync();
+        const long long row0 = tile * R;
+        const int nrows = (int)min((long long)R, p.rows - row0);
+        const int nblk = nrows * (L >> 3);
+        const unsigned long long blk0 = ((p.first_row + (unsigned long long)row0) * (unsigned long long)L) >> 3;
+        const uint32_t mb = s_mask + b * tile_mask_bytes;
+        if (ok) {
+          for (int i0 = rt; i0 < nblk; i0 += 4 * RNG_WARPS * 32) {
+            unsigned long long blk[4];
+            uint32_t o[4][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) blk[q] = blk0 + (unsigned)(i0 + q * RNG_WARPS * 32);   // surplus blocks are discarded
+            philox_blocks<4>(blk, p.key, o);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int i = i0 + q * RNG_WARPS * 32;
+              if (i < nblk) {
+                uint32_t km[4];
+                masks_from_words<true>(p, o[q], km);
+                uint2 bytes;
+                bytes.x = __byte_perm(km[0], km[1], 0x6420) & 0x01010101u;
+                bytes.y = __byte_perm(km[2], km[3], 0x6420) & 0x01010101u;
+                sts8(mb + (uint32_t)i * 8u, bytes);
+              }
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        rng_warps_sync();
+        if (rt == 0) {
+          if (ok && nrows > 0) {
+            bulk_store(p.mask + row0 * (long long)L, mb, (uint32_t)nrows * (uint32_t)L);
+            bulk_commit_group();
+          }
+          mbar_arrive(mfull_bar(b));
+        }
+      }
+      if (rt == 0) bulk_wait_all();
+    }
+  } else {
+    // --------------------------------------------------------------- consumers
+    bool valid[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) valid[c] = (lane + 32 * c) * 8 < L;
+    char* out = static_cast<char*>(p.out);
+    const uint32_t my_out = s_out + warp * 2 * wbuf_bytes;
+    uint32_t stage = 0, phase = 0, buf = 0, it = 0;
+    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const long long row0 = tile * R + warp * RPW;       // first of this warp's rows
+      const int nrows = (int)max(0ll, min((long long)RPW, p.rows - row0));
+      if (!mbar_wait(full_bar(stage), phase, abort_flag, status, kWdStreamFull)) break;
+      Unit<T> cur[RPW][CH];
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        const uint32_t base = s_in + stage * tile_bytes + (warp * RPW + r) * row_bytes;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          if (valid[c] && r < nrows) unit_from_smem<T>(cur[r][c], base + (lane + 32 * c) * 8 * (uint32_t)sizeof(T));
+          else cur[r][c].fill_neg_inf();
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(stage));       // the rows are in registers: the stage may be refilled
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+
+      // the staging buffer about to be written was handed to the copy engine two tiles ago
+      if (lane == 0) bulk_wait_read_le1();
+      __syncwarp();
+      const uint32_t ob = my_out + buf * wbuf_bytes, mbw = ob + wout_bytes;
+      const uint32_t mbuf = it % MASK_BUFS;
+      const uint32_t mtile = s_mask + mbuf * tile_mask_bytes + (uint32_t)(warp * RPW) * (uint32_t)L;
+      bool mask_ready = !DROP;
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) {
+        if (r < nrows) {
+          uint64_t e2[CH][4];
+          const uint64_t g2 = row_exponentials<T, CH, EXT>(p, cur[r], row0 + r, lane, e2);
+          if constexpr (DROP) {
+            if (!mask_ready) {       // as late as possible: the generator works while the exponentials are computed
+              mask_ready = mbar_wait(mfull_bar(mbuf), (it / MASK_BUFS) & 1u, abort_flag, status, kWdMaskFull);
+              if (!mask_ready) break;
+            }
+          }
+#pragma unroll
+          for (int c = 0; c < CH; ++c) {
+            if (valid[c]) {
+              uint32_t km[4];
+              if constexpr (DROP) masks_from_bytes(lds8(mtile + r * L + (lane + 32 * c) * 8), km);
+              else masks_from_words<false>(p, km, km);
+              finish_unit_smem<T, !DROP>(e2[c], g2, ob + r * row_bytes + (lane + 32 * c) * 8 * (uint32_t)sizeof(T),
+                                         mbw + r * L + (lane + 32 * c) * 8, km);
+            }
+          }
+        }
+      }
+      if constexpr (DROP) {
+        if (nrows > 0 && !mask_ready) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(mempty_bar(mbuf));     // this warp is done with the tile's mask buffer
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0 && nrows > 0) {
+        bulk_store(out + row0 * (long long)row_bytes, ob, (uint32_t)nrows * row_bytes);
+        if constexpr (!DROP) bulk_store(p.mask + row0 * (long long)L, mbw, (uint32_t)nrows * (uint32_t)L);
+        bulk_commit_group();
+      }
+      buf ^= 1u;
+    }
+    if (lane == 0) bulk_wait_all();
+  }
+}
+
+}  // namespace stream
 
 // -------------------------------------------------------- CTA-per-row kernel
 // Three passes over the row (the second and third are served by L2).  VEC = 8
@@ -534,6 +839,358 @@ __global__ void __launch_bounds__(256) softmax_block_kernel(const SmParams p) {
   }
 }
 
+// ------------------------------------------- long rows: shared-memory resident
+// One CTA of 8 warps per row.  The row (contiguous in memory) is brought into
+// shared memory once by the copy engine (cp.async.bulk, completion counted on an
+// mbarrier); the three sweeps -- maximum, sum of exponentials, normalise / drop /
+// store -- then read shared memory, so the row crosses HBM once in each
+// direction.  With two row buffers the next row of the CTA is in flight while the
+// current one is processed.  Unit u belongs to thread u % 256 and every sum
+// follows the order of softmax_block_kernel<T, 8, ...>, so the two kernels
+// produce the same bits (the CPU restatement of that schedule covers both).
+namespace longrow {
+
+constexpr int THREADS = 256;
+enum : int { kWdRowFull = 311 };
+
+// UPT > 0: rows of at most UPT * 2048 elements; a thread's units are read from
+// shared memory once and stay in registers through the three steps, and every
+// exponential is computed once.  UPT = 0: any length, three sweeps over shared
+// memory.  Same order of operations either way.
+template <typename T, int UPT, bool DROP, bool EXT>
+__global__ void __launch_bounds__(THREADS) softmax_smem_row_kernel(const SmParams p, int nbuf, int* status) {
+  constexpr bool HF = sizeof(T) == 2 && !EXT;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ float red[8];
+  __shared__ __align__(8) uint64_t bar_store[2];
+  __shared__ int abort_word;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int L = p.L;
+  const int units = L / 8;
+  const uint32_t row_bytes = (uint32_t)L * (uint32_t)sizeof(T);
+  const uint32_t buf_bytes = (row_bytes + 127u) & ~127u;
+  const uint32_t s_rows = smem_u32(smem);
+  const uint32_t bar0 = smem_u32(bar_store);
+  volatile int* abort_flag = &abort_word;
+  const char* in = static_cast<const char*>(p.in);
+  T* out = static_cast<T*>(p.out);
+
+  if (tid == 0) {
+    for (int b = 0; b < nbuf; ++b) mbar_init(bar0 + 8u * b, 1);
+    abort_word = 0;
+    mbar_fence_init();
+    // prologue: the first nbuf rows of this CTA
+    for (int b = 0; b < nbuf; ++b) {
+      const long long r = (long long)blockIdx.x + (long long)b * gridDim.x;
+      if (r < p.rows) {
+        mbar_arrive_expect_tx(bar0 + 8u * b, row_bytes);
+        stream::bulk_load(s_rows + b * buf_bytes, in + r * (long long)row_bytes, row_bytes, bar0 + 8u * b);
+      }
+    }
+  }
+  __syncthreads();
+
+  uint32_t it = 0;
+  for (long long row = blockIdx.x; row < p.rows; row += gridDim.x, ++it) {
+    const uint32_t b = it % (uint32_t)nbuf, parity = (it / (uint32_t)nbuf) & 1u;
+    if (!mbar_wait(bar0 + 8u * b, parity, abort_flag, status, kWdRowFull)) break;
+    const uint32_t xs = s_rows + b * buf_bytes;
+    const int len = valid_length<EXT>(p, row);
+
+    if constexpr (UPT > 0) {
+      // ---- register-resident form
+      Unit<T> un[UPT];
+      float m = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < UPT; ++j) {
+        const int u = tid + j * THREADS;
+        if (u < units) {
+          stream::unit_from_smem<T>(un[j], xs + (uint32_t)u * 8u * (uint32_t)sizeof(T));
+          float x[8]; un[j].widen(x);
+          adjust8<EXT>(x, u * 8, len, p.scale);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
+        }
+      }
+      __syncthreads();                        // every thread holds its part of the row: the buffer is free
+      if (tid == 0) {
+        const long long nr = row + (long long)nbuf * gridDim.x;
+        if (nr < p.rows) {
+          mbar_arrive_expect_tx(bar0 + 8u * b, row_bytes);
+          stream::bulk_load(xs, in + nr * (long long)row_bytes, row_bytes, bar0 + 8u * b);
+        }
+      }
+      // dropout decisions of this thread's units, four Philox blocks at a time
+      uint32_t km[UPT][4];
+      {
+        const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)L) >> 3;
+        constexpr int NB = UPT < 4 ? UPT : 4;
+#pragma unroll
+        for (int j0 = 0; j0 < UPT; j0 += NB) {
+          if (DROP) {
+            unsigned long long blk[NB];
+            uint32_t o[NB][4];
+#pragma unroll
+            for (int q = 0; q < NB; ++q) blk[q] = blk0 + (unsigned)(tid + (j0 + q) * THREADS);
+            philox_blocks<NB>(blk, p.key, o);
+#pragma unroll
+            for (int q = 0; q < NB; ++q) masks_from_words<true>(p, o[q], km[j0 + q]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < NB; ++q) masks_from_words<false>(p, km[j0 + q], km[j0 + q]);
+          }
+        }
+      }
+      m = warp_max(m);
+      if (lane == 0) red[warp] = m;
+      __syncthreads();
+      m = red[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+      __syncthreads();
+      const bool all_masked = m == -INFINITY;
+      if (all_masked) m = 0.0f;
+      const ExpCtx ctx = make_exp_ctx<HF>(m);
+      uint64_t e2[UPT][4];
+      uint64_t s2 = pack2(0.0f, 0.0f);
+#pragma unroll
+      for (int j = 0; j < UPT; ++j) {
+        const int u = tid + j * THREADS;
+        if (u < units) {
+          float x[8]; un[j].widen(x);
+          adjust8<EXT>(x, u * 8, len, p.scale);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            e2[j][k] = exp_pair<HF>(x[2 * k], x[2 * k + 1], ctx);
+            s2 = add2(s2, e2[j][k]);
+          }
+        }
+      }
+      const float2 sp = unpack2(s2);
+      const float lane_sum = warp_sum_butterfly(__fadd_rn(sp.x, sp.y));
+      if (lane == 0) red[warp] = lane_sum;
+      __syncthreads();
+      float total = red[0];
+#pragma unroll
+      for (int w = 1; w < 8; ++w) total = __fadd_rn(total, red[w]);
+      __syncthreads();                        // red[] is reused by the next row
+      const float inv = (total == 0.0f || all_masked) ? 0.0f : __fdiv_rn(1.0f, total);
+      const float g = __fmul_rn(inv, p.keep_scale);
+      const uint64_t g2 = pack2(g, g);
+#pragma unroll
+      for (int j = 0; j < UPT; ++j) {
+        const int u = tid + j * THREADS;
+        if (u < units) {
+          const long long off = row * L + (long long)u * 8;
+          finish_unit_masked<T, DROP>(e2[j], g2, out + off, p.mask + off, km[j]);
+        }
+      }
+      continue;
+    }
+
+    // ---- three sweeps over shared memory
+    // sweep 1: maximum
+    float m = -INFINITY;
+    for (int u = tid; u < units; u += THREADS) {
+      Unit<T> un; stream::unit_from_smem<T>(un, xs + (uint32_t)u * 8u * (uint32_t)sizeof(T));
+      float x[8]; un.widen(x);
+      adjust8<EXT>(x, u * 8, len, p.scale);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, x[i]);
+    }
+    m = warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    const bool all_masked = m == -INFINITY;
+    if (all_masked) m = 0.0f;
+    const ExpCtx ctx = make_exp_ctx<HF>(m);
+
+    // sweep 2: sum of exponentials
+    uint64_t s2 = pack2(0.0f, 0.0f);
+    for (int u = tid; u < units; u += THREADS) {
+      Unit<T> un; stream::unit_from_smem<T>(un, xs + (uint32_t)u * 8u * (uint32_t)sizeof(T));
+      float x[8]; un.widen(x);
+      adjust8<EXT>(x, u * 8, len, p.scale);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) s2 = add2(s2, exp_pair<HF>(x[2 * k], x[2 * k + 1], ctx));
+    }
+    const float2 sp = unpack2(s2);
+    float lane_sum = warp_sum_butterfly(__fadd_rn(sp.x, sp.y));
+    if (lane == 0) red[warp] = lane_sum;
+    __syncthreads();
+    float total = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) total = __fadd_rn(total, red[w]);
+    const float inv = (total == 0.0f || all_masked) ? 0.0f : __fdiv_rn(1.0f, total);
+    const float g = __fmul_rn(inv, p.keep_scale);
+    const uint64_t g2 = pack2(g, g);
+
+    // sweep 3: normalise, drop, store
+    const unsigned long long idx0 = (p.first_row + (unsigned long long)row) * (unsigned long long)L;
+    for (int u = tid; u < units; u += THREADS) {
+      Unit<T> un; stream::unit_from_smem<T>(un, xs + (uint32_t)u * 8u * (uint32_t)sizeof(T));
+      float x[8]; un.widen(x);
+      adjust8<EXT>(x, u * 8, len, p.scale);
+      uint64_t e2[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) e2[k] = exp_pair<HF>(x[2 * k], x[2 * k + 1], ctx);
+      const long long off = row * L + (long long)u * 8;
+      finish_unit<T, DROP>(e2, g2, out + off, p.mask + off, p, (idx0 >> 3) + (unsigned)u);
+    }
+    __syncthreads();     // every thread is done with this buffer (and with red[])
+    if (tid == 0) {
+      const long long nr = row + (long long)nbuf * gridDim.x;
+      if (nr < p.rows) {
+        mbar_arrive_expect_tx(bar0 + 8u * b, row_bytes);
+        stream::bulk_load(xs, in + nr * (long long)row_bytes, row_bytes, bar0 + 8u * b);
+      }
+    }
+  }
+}
+
+// --------------------------------------------- long rows: online single pass
+// Rows too long for shared memory.  Sweep 1 reads the row once and keeps, per
+// thread, a running maximum m_t and a sum of exponentials relative to it,
+// rescaled by 2^((m_old - m_new) log2 e) whenever a unit raises the maximum
+// (a unit whose elements are all -inf is skipped).  The threads' pairs (m_t, s_t)
+// are then brought to the row maximum and added in the fixed order (xor
+// butterfly per warp, warps ascending).  Sweep 2 reads the row again to write
+// e_j * g.  FP32-storage arithmetic for both storage types.
+template <typename T, bool DROP, bool EXT>
+__global__ void __launch_bounds__(THREADS) softmax_online_kernel(const SmParams p) {
+  __shared__ float red[8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int L = p.L;
+  const int units = L / 8;
+  const T* in = static_cast<const T*>(p.in);
+  T* out = static_cast<T*>(p.out);
+  const uint64_t log2e2 = pack2(kLog2e, kLog2e);
+
+  for (long long row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    const T* xr = in + row * L;
+    const int len = valid_length<EXT>(p, row);
+    float mt = -INFINITY;
+    uint64_t s2 = pack2(0.0f, 0.0f);
+    uint64_t negc2 = pack2(0.0f, 0.0f);
+    for (int u = tid; u < units; u += THREADS) {
+      Unit<T> un; un.load(xr + u * 8);
+      float x[8]; un.widen(x);
+      adjust8<EXT>(x, u * 8, len, p.scale);
+      float mu = x[0];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) mu = fmaxf(mu, x[i]);
+      if (mu == -INFINITY) continue;                 // contributes nothing
+      if (mu > mt) {
+        const float negc = -__fmul_rn(mu, kLog2e);
+        if (mt != -INFINITY) {
+          const float t = fmaxf(__fmaf_rn(mt, kLog2e, negc), -127.0f);
+          const float2 f = unpack2(exp2_pair(pack2(t, t)));
+          s2 = mul2(s2, pack2(f.x, f.x));
+        }
+        mt = mu;
+        negc2 = pack2(negc, negc);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 t = unpack2(fma2(pack2(x[2 * k], x[2 * k + 1]), log2e2, negc2));
+        s2 = add2(s2, exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f))));
+      }
+    }
+    // row maximum
+    float m = warp_max(mt);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+    __syncthreads();
+    const bool all_masked = m == -INFINITY;
+    if (all_masked) m = 0.0f;
+    const float negc = -__fmul_rn(m, kLog2e);
+    // this thread's sum relative to the row maximum
+    const float2 sp = unpack2(s2);
+    float st = __fadd_rn(sp.x, sp.y);
+    if (mt == -INFINITY) st = 0.0f;
+    else {
+      const float t = fmaxf(__fmaf_rn(mt, kLog2e, negc), -127.0f);
+      st = __fmul_rn(st, unpack2(exp2_pair(pack2(t, t))).x);
+    }
+    st = warp_sum_butterfly(st);
+    if (lane == 0) red[warp] = st;
+    __syncthreads();
+    float total = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) total = __fadd_rn(total, red[w]);
+    __syncthreads();
+    const float inv = (total == 0.0f || all_masked) ? 0.0f : __fdiv_rn(1.0f, total);
+    const float g = __fmul_rn(inv, p.keep_scale);
+    const uint64_t g2 = pack2(g, g);
+    const uint64_t rowc2 = pack2(negc, negc);
+
+    const unsigned long long idx0 = (p.first_row + (unsigned long long)row) * (unsigned long long)L;
+    for (int u = tid; u < units; u += THREADS) {
+      Unit<T> un; un.load(xr + u * 8);
+      float x[8]; un.widen(x);
+      adjust8<EXT>(x, u * 8, len, p.scale);
+      uint64_t e2[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 t = unpack2(fma2(pack2(x[2 * k], x[2 * k + 1]), log2e2, rowc2));
+        e2[k] = exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f)));
+      }
+      const long long off = row * L + (long long)u * 8;
+      finish_unit<T, DROP>(e2, g2, out + off, p.mask + off, p, (idx0 >> 3) + (unsigned)u);
+    }
+  }
+}
+
+}  // namespace longrow
+
+// Largest row that the shared-memory resident kernel takes (one buffer).
+constexpr size_t kSmemRowLimit = 200 * 1024;
+
+template <typename T, bool DROP, bool EXT>
+void launch_smem_row_t(const SmParams& p, int sms, cudaStream_t stream) {
+  const size_t row_bytes = (size_t)p.L * sizeof(T);
+  const size_t buf = (row_bytes + 127) & ~(size_t)127;
+  const int nbuf = 2 * buf <= 100 * 1024 ? 2 : 1;
+  const size_t smem = nbuf * buf;
+  const int units_per_thread = (p.L / 8 + longrow::THREADS - 1) / longrow::THREADS;
+  void (*kern)(const SmParams, int, int*) =
+      units_per_thread <= 2   ? longrow::softmax_smem_row_kernel<T, 2, DROP, EXT>
+      : units_per_thread <= 4 ? longrow::softmax_smem_row_kernel<T, 4, DROP, EXT>
+      : units_per_thread <= 8 ? longrow::softmax_smem_row_kernel<T, 8, DROP, EXT>
+                              : longrow::softmax_smem_row_kernel<T, 0, DROP, EXT>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  int per_sm = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, longrow::THREADS, smem);
+  if (per_sm < 1) per_sm = 1;
+  const long long cap = (long long)sms * per_sm;
+  const int grid = (int)(p.rows < cap ? p.rows : cap);
+  kern<<<grid, longrow::THREADS, smem, stream>>>(p, nbuf, watchdog_word());
+}
+template <typename T, bool DROP, bool EXT>
+void launch_online_t(const SmParams& p, int sms, cudaStream_t stream) {
+  const long long cap = (long long)sms * 8;
+  const int grid = (int)(p.rows < cap ? p.rows : cap);
+  longrow::softmax_online_kernel<T, DROP, EXT><<<grid, longrow::THREADS, 0, stream>>>(p);
+}
+template <typename T>
+void launch_long(const SmParams& p, bool drop, bool ext, bool online, int sms, cudaStream_t stream) {
+#define TFB_LONG(DROP, EXT)                                              \
+  do {                                                                   \
+    if (online) launch_online_t<T, DROP, EXT>(p, sms, stream);           \
+    else launch_smem_row_t<T, DROP, EXT>(p, sms, stream);                \
+  } while (0)
+  if (ext) { if (drop) TFB_LONG(true, true); else TFB_LONG(false, true); }
+  else { if (drop) TFB_LONG(true, false); else TFB_LONG(false, false); }
+#undef TFB_LONG
+}
+
 template <typename T, int CH, bool DROP, bool EXT>
 void launch_warp_t(const SmParams& p, int sms, cudaStream_t stream) {
   const long long ctas_needed = (p.rows + 7) / 8;
@@ -555,6 +1212,61 @@ void launch_warp(const SmParams& p, bool drop, bool ext, int sms, cudaStream_t s
   }
 }
 
+// Streaming kernel: needs whole 16-byte mask rows (L % 16 == 0, 16-byte aligned
+// mask pointer) and rows of at most 4 KB.
+template <typename T, int CH, bool DROP, bool EXT>
+void launch_stream_t(const SmParams& p, int sms, cudaStream_t stream) {
+  using C = stream::Cfg<T, CH>;
+  const size_t row_bytes = (size_t)p.L * sizeof(T);
+  constexpr int kThreads = stream::Threads<DROP>::value;
+  const size_t smem = stream::STAGES * C::R * row_bytes +
+                      (size_t)stream::WARPS * 2 * C::RPW * (row_bytes + (DROP ? 0 : p.L)) +
+                      (DROP ? (size_t)stream::MASK_BUFS * C::R * p.L : 0) +
+                      8 * (2 * stream::STAGES + 2 * stream::MASK_BUFS) + 16;
+  auto kern = stream::softmax_stream_kernel<T, CH, DROP, EXT>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  int per_sm = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+  if (per_sm < 1) per_sm = 1;
+  const long long tiles = (p.rows + C::R - 1) / C::R;
+  const long long cap = (long long)sms * per_sm;
+  const int grid = (int)(tiles < cap ? tiles : cap);
+  kern<<<grid, kThreads, smem, stream>>>(p, watchdog_word());
+}
+template <typename T, int CH>
+void launch_stream(const SmParams& p, bool drop, bool ext, int sms, cudaStream_t stream) {
+  if (ext) {
+    if (drop) launch_stream_t<T, CH, true, true>(p, sms, stream);
+    else launch_stream_t<T, CH, false, true>(p, sms, stream);
+  } else {
+    if (drop) launch_stream_t<T, CH, true, false>(p, sms, stream);
+    else launch_stream_t<T, CH, false, false>(p, sms, stream);
+  }
+}
+
+// 0 = choose by shape, 1 = warp kernel only, 2 = streaming kernel wherever it is eligible.
+// TENSORFUSE_B200_SOFTMAX_FORM=warp|stream, read once; meant for measurements and tests.
+int softmax_form_override() {
+  static const int form = [] {
+    const char* e = getenv("TENSORFUSE_B200_SOFTMAX_FORM");
+    if (e == nullptr) return 0;
+    if (strcmp(e, "warp") == 0) return 1;
+    if (strcmp(e, "stream") == 0) return 2;
+    return 0;
+  }();
+  return form;
+}
+
+template <typename T>
+bool stream_eligible(const SmParams& p) {
+  if (p.L % 16 != 0 || ((uintptr_t)p.mask & 15u) != 0) return false;
+  if ((size_t)p.L * sizeof(T) > 4096) return false;
+  const int form = softmax_form_override();
+  if (form == 1) return false;
+  if (form == 2) return true;
+  return p.rows >= 4096;     // small problems: the plain kernel has less set-up
+}
+
 template <typename T, int VEC>
 void launch_block(const SmParams& p, bool drop, bool ext, int warps, int sms, cudaStream_t stream) {
   const long long cap = (long long)sms * (warps == 1 ? 32 : 8);
@@ -570,11 +1282,18 @@ void launch_block(const SmParams& p, bool drop, bool ext, int warps, int sms, cu
 
 template <typename T>
 void dispatch(const SmParams& p, bool drop, bool ext, SoftmaxSchedule sch, int sms, cudaStream_t stream) {
-  if (sch.vec == 8 && sch.warps == 1) {
+  if (sch.vec == 8 && sch.warps == 1 && stream_eligible<T>(p)) {
+    if (p.L <= 256) launch_stream<T, 1>(p, drop, ext, sms, stream);
+    else if (p.L <= 512) launch_stream<T, 2>(p, drop, ext, sms, stream);
+    else if (p.L <= 1024) launch_stream<T, 4>(p, drop, ext, sms, stream);
+    else launch_stream<T, 8>(p, drop, ext, sms, stream);
+  } else if (sch.vec == 8 && sch.warps == 1) {
     if (p.L <= 256) launch_warp<T, 1>(p, drop, ext, sms, stream);
     else if (p.L <= 512) launch_warp<T, 2>(p, drop, ext, sms, stream);
     else if (p.L <= 1024) launch_warp<T, 4>(p, drop, ext, sms, stream);
     else launch_warp<T, 8>(p, drop, ext, sms, stream);
+  } else if (sch.vec == 8 && sch.warps == 8 && softmax_form_override() != 1) {
+    launch_long<T>(p, drop, ext, sch.online != 0, sms, stream);
   } else if (sch.vec == 8) {
     launch_block<T, 8>(p, drop, ext, sch.warps, sms, stream);
   } else {
@@ -598,11 +1317,13 @@ int sm_count_of_current_device() {
 }  // namespace
 
 SoftmaxSchedule softmax_schedule(int L, int dtype, bool aligned16) {
-  (void)dtype;
   SoftmaxSchedule s;
+  s.online = 0;
   if (aligned16 && L % 8 == 0) {
     s.vec = 8;
     s.warps = L <= 2048 ? 1 : 8;
+    // rows beyond the shared-memory resident kernel: one online sweep + one write sweep
+    if ((size_t)L * (dtype == kF16 ? 2 : 4) > kSmemRowLimit) s.online = 1;
   } else {
     s.vec = 1;
     s.warps = L <= 1024 ? 1 : 8;

@@ -123,13 +123,43 @@ extern "C" TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseT
   const size_t wrow = (size_t)H * es;
   const TensorFuseTensor* wq[3] = {p->query_weight, p->key_weight, p->value_weight};
   const TensorFuseTensor* bq[3] = {p->query_bias, p->key_bias, p->value_bias};
+  auto concatenate = [&](char* wdst, char* bdst) {
+    for (int i = 0; i < 3; ++i) {
+      cuda_step(cudaMemcpy2DAsync(wdst + i * wrow, 3 * wrow, wq[i]->data, wrow, wrow, (size_t)H,
+                                  cudaMemcpyDeviceToDevice, stream));
+      if (p->use_bias) cuda_step(cudaMemcpyAsync(bdst + i * wrow, bq[i]->data, wrow, cudaMemcpyDeviceToDevice, stream));
+    }
+  };
+  // Weights registered as immutable (tensorfuse_b200_register_weights on the three
+  // device matrices): the concatenation is built once per device and kept.
+  const char* w_qkv = wcat;
+  const char* b_qkv = bcat;
+  bool fresh = false;
+  Runtime::FusedQkv* slot = Runtime::get().fused_qkv_slot(pool_dev, wq[0]->data, wq[1]->data, wq[2]->data, &fresh);
   if (!p->use_bias) cuda_step(cudaMemsetAsync(bcat, 0, bcat_bytes, stream));
-  for (int i = 0; i < 3; ++i) {
-    cuda_step(cudaMemcpy2DAsync(wcat + i * wrow, 3 * wrow, wq[i]->data, wrow, wrow, (size_t)H,
-                                cudaMemcpyDeviceToDevice, stream));
-    if (p->use_bias) cuda_step(cudaMemcpyAsync(bcat + i * wrow, bq[i]->data, wrow, cudaMemcpyDeviceToDevice, stream));
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(stream, &capturing);
+  const bool must_build = slot != nullptr && (fresh || slot->w_bytes != wcat_bytes || slot->b_bytes != bcat_bytes);
+  if (must_build && capturing != cudaStreamCaptureStatusNone) slot = nullptr;   // building synchronises: not inside a capture
+  if (slot != nullptr && p->use_bias) {
+    if (must_build) {
+      if (slot->w) cudaFree(slot->w);
+      if (slot->b) cudaFree(slot->b);
+      slot->w = slot->b = nullptr;
+      if (cudaMalloc(&slot->w, wcat_bytes) == cudaSuccess && cudaMalloc(&slot->b, bcat_bytes) == cudaSuccess) {
+        slot->w_bytes = wcat_bytes; slot->b_bytes = bcat_bytes;
+        concatenate(static_cast<char*>(slot->w), static_cast<char*>(slot->b));
+        cudaStreamSynchronize(stream);    // later calls may come on other streams
+      } else {
+        cudaGetLastError();
+        if (slot->w) cudaFree(slot->w);
+        slot->w = slot->b = nullptr; slot->w_bytes = slot->b_bytes = 0;
+      }
+    }
+    if (slot->w != nullptr) { w_qkv = static_cast<const char*>(slot->w); b_qkv = static_cast<const char*>(slot->b); }
   }
-  step(gemm(input->data, wcat, bcat, qkv, M, 3 * H, H, kdt, kEpiLinear, beta, stream));
+  if (w_qkv == wcat) concatenate(wcat, bcat);
+  step(gemm(input->data, w_qkv, b_qkv, qkv, M, 3 * H, H, kdt, kEpiLinear, beta, stream));
   if (r == kOk) {
     AttnArgs a{};
     a.q = qkv; a.k = qkv + wrow; a.v = qkv + 2 * wrow; a.out = ctx;

@@ -86,13 +86,24 @@ def test_reference_package_imports_without_stub_fallback():
     assert rc == 0, out[-3000:]
 
 
-@pytest.mark.parametrize("test_file", ["test_mathematical_verification.py", "test_int8_tensor_cores.py",
-                                       "test_core_bindings.py", "test_numpy_integration.py"])
+# file -> tests that skip themselves whatever the library does:
+#   test_mathematical_verification.py:179 skips its alpha/beta case unconditionally;
+#   test_numpy_integration.py:72 skips when numpy has no bfloat16.
+# Any other skip means the test gave up on the library ("GPU not available: ...").
+PY_TESTS = {"test_mathematical_verification.py": 1, "test_int8_tensor_cores.py": 0,
+            "test_core_bindings.py": 0, "test_numpy_integration.py": 1}
+
+
+@pytest.mark.parametrize("test_file", sorted(PY_TESTS))
 def test_reference_python_tests(test_file):
     """The reference's Python tests against the reference's package over this library."""
+    import re
     path = os.path.join(OUT, "py", "tests", test_file)
     assert os.path.exists(path)
-    rc, out = _run([sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider", path],
+    rc, out = _run([sys.executable, "-m", "pytest", "-q", "-rs", "-p", "no:cacheprovider", path],
                    cwd=os.path.join(OUT, "py", "tests"), env=_pyenv(), timeout=1200)
     assert rc == 0, out[-6000:]
-    assert " passed" in out and " skipped" not in out.splitlines()[-1], out[-1500:]
+    summary = out.strip().splitlines()[-1]
+    passed = int(re.search(r"(\d+) passed", summary).group(1))
+    skipped = int(m.group(1)) if (m := re.search(r"(\d+) skipped", summary)) else 0
+    assert passed >= 3 and skipped <= PY_TESTS[test_file] and "failed" not in summary, out[-3000:]
