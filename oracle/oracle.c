@@ -211,11 +211,11 @@ void tfo_softmax_ref_f16(const uint16_t* in, uint16_t* out, uint8_t* mask, long 
 }
 
 /* ---------------------------------------------------------------- Philox
- * Philox4x32 with 10 rounds (Salmon et al., SC'11), multipliers 0xD2511F53 /
+ * Philox4x32 (Salmon et al., SC'11) with a selectable number of rounds, multipliers 0xD2511F53 /
  * 0xCD9E8D57, Weyl key increments 0x9E3779B9 / 0xBB67AE85. */
-void tfo_philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
-                       uint32_t k1, uint32_t out[4]) {
-  for (int r = 0; r < 10; ++r) {
+void tfo_philox4x32_r(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                      uint32_t k1, int rounds, uint32_t out[4]) {
+  for (int r = 0; r < rounds; ++r) {
     uint64_t p0 = (uint64_t)0xD2511F53u * c0;
     uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
     uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0;
@@ -227,6 +227,14 @@ void tfo_philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint3
   }
   out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
 }
+/* The 10-round generator of the Random123 distribution (known-answer vectors). */
+void tfo_philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0,
+                       uint32_t k1, uint32_t out[4]) {
+  tfo_philox4x32_r(c0, c1, c2, c3, k0, k1, 10, out);
+}
+/* Rounds of the library's dropout stream: 7, the fewest rounds for which the
+ * Philox paper reports a clean BigCrush (tensorfuse_b200/csrc/philox.cuh). */
+#define TFO_DROPOUT_ROUNDS 7
 
 /* Dropout decision for the element with global flat index idx: eight
  * consecutive elements share one Philox block (counter = idx/8, key = seed);
@@ -243,8 +251,8 @@ uint32_t tfo_dropout_threshold(float p) {
 static inline int dropout_keep(uint64_t idx, uint64_t seed, uint32_t thr) {
   uint32_t o[4];
   uint64_t blk = idx >> 3;
-  tfo_philox4x32_10((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u, (uint32_t)seed,
-                    (uint32_t)(seed >> 32), o);
+  tfo_philox4x32_r((uint32_t)blk, (uint32_t)(blk >> 32), 0u, 0u, (uint32_t)seed,
+                   (uint32_t)(seed >> 32), TFO_DROPOUT_ROUNDS, o);
   uint32_t e = (uint32_t)(idx & 7u);
   uint32_t field = (o[e >> 1] >> (16u * (e & 1u))) & 0x7FFFu;
   return field >= thr;

@@ -23,7 +23,7 @@
 // packed fma/add/mul.f32x2 instructions of sm_100 keep the instruction count of
 // that polynomial close to a MUFU-based one.
 //
-// Dropout uses Philox4x32-10: eight consecutive elements share one block
+// Dropout uses Philox4x32 with 7 rounds (philox.cuh): eight consecutive elements share one block
 // (counter = global element index / 8, key = seed), each element takes a 16-bit
 // field and is kept when its low 15 bits are >= round(p * 32768).  The counter depends only on
 // the element's position in the whole tensor, so any row-sharding across GPUs
@@ -395,6 +395,116 @@ __device__ __forceinline__ uint64_t row_exponentials(const SmParams& p, const Un
   return pack2(g, g);
 }
 
+// The same for NR rows in lockstep: every step is carried out for all rows before
+// the next one starts, so that a warp always has NR independent dependency
+// chains (shuffle reductions, polynomial evaluations) in flight.  Row for row
+// the operations and their order are those of row_exponentials.
+template <typename T, int CH, bool EXT, int NR>
+__device__ __forceinline__ void rows_exponentials(const SmParams& p, const Unit<T> (&cur)[NR][CH],
+                                                  const long long (&row)[NR], int lane, uint64_t (&e2)[NR][CH][4],
+                                                  uint64_t (&g2)[NR]) {
+  constexpr bool HF = sizeof(T) == 2 && !EXT;
+  int len[NR];
+  float m[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) len[r] = valid_length<EXT>(p, row[r]);
+  if constexpr (HF) {
+    uint32_t m2[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      m2[r] = 0xFC00FC00u;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const uint4 v = cur[r][c].raw;
+        m2[r] = hmax2_bits(hmax2_bits(m2[r], hmax2_bits(v.x, v.y)), hmax2_bits(v.z, v.w));
+      }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) m2[r] = hmax2_bits(m2[r], __shfl_xor_sync(0xffffffffu, m2[r], off));
+    }
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      const float2 mf = __half22float2(*reinterpret_cast<const __half2*>(&m2[r]));
+      m[r] = fmaxf(mf.x, mf.y);
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      m[r] = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        float x[8];
+        cur[r][c].widen(x);
+        adjust8<EXT>(x, (lane + 32 * c) * 8, len[r], p.scale);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) m[r] = fmaxf(m[r], x[i]);
+      }
+    }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) m[r] = fmaxf(m[r], __shfl_xor_sync(0xffffffffu, m[r], off));
+    }
+  }
+  bool all_masked[NR];
+  ExpCtx ctx[NR];
+  uint64_t s2[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    all_masked[r] = m[r] == -INFINITY;
+    if (all_masked[r]) m[r] = 0.0f;
+    ctx[r] = make_exp_ctx<HF>(m[r]);
+    s2[r] = pack2(0.0f, 0.0f);
+  }
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      if constexpr (HF) {
+        const __half lo_h = __float2half_rn(ctx[r].lo);
+        const __half2 lo2 = __halves2half2(lo_h, lo_h);
+        const uint32_t lo_bits = *reinterpret_cast<const uint32_t*>(&lo2);
+        const uint32_t w[4] = {cur[r][c].raw.x, cur[r][c].raw.y, cur[r][c].raw.z, cur[r][c].raw.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t xw = hmax2_bits(w[k], lo_bits);
+          const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw));
+          e2[r][c][k] = exp_pair<true, true>(f.x, f.y, ctx[r]);
+          s2[r] = add2(s2[r], e2[r][c][k]);
+        }
+      } else {
+        float x[8];
+        cur[r][c].widen(x);
+        adjust8<EXT>(x, (lane + 32 * c) * 8, len[r], p.scale);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          e2[r][c][k] = exp_pair<false>(x[2 * k], x[2 * k + 1], ctx[r]);
+          s2[r] = add2(s2[r], e2[r][c][k]);
+        }
+      }
+    }
+  }
+  float total[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    const float2 sp = unpack2(s2[r]);
+    total[r] = __fadd_rn(sp.x, sp.y);
+  }
+#pragma unroll
+  for (int off = 16; off >= 1; off >>= 1) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) total[r] = __fadd_rn(total[r], __shfl_xor_sync(0xffffffffu, total[r], off));
+  }
+#pragma unroll
+  for (int r = 0; r < NR; ++r) {
+    const float inv = (total[r] == 0.0f || all_masked[r]) ? 0.0f : __fdiv_rn(1.0f, total[r]);
+    const float g = __fmul_rn(inv, p.keep_scale);
+    g2[r] = pack2(g, g);
+  }
+}
+
 // CH = units per lane (row length <= 256*CH).  8 warps per CTA, grid-stride
 // over rows, next row's loads in flight while the current row is processed.
 template <typename T, int CH, bool DROP, bool EXT>
@@ -444,38 +554,27 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const SmParams p) {
 }
 
 // ----------------------------------------------------- streaming (bulk-copy) kernel
-// The same per-row arithmetic, fed by the copy engine instead of by the warps'
-// own loads.  Rows are dense, so a tile of R consecutive rows is one contiguous
-// byte range:
+// The dropout-free kernel for large problems: the same per-row arithmetic, fed
+// by the copy engine instead of by the warps' own loads.  Rows are dense, so a
+// tile of R consecutive rows is one contiguous byte range:
 //   * a producer warp streams tiles into a ring of shared-memory stages with
 //     cp.async.bulk (completion counted in bytes on an mbarrier);
-//   * eight consumer warps take RPW rows each out of a stage, release it as soon
-//     as the rows are in registers, and write their results into their own
-//     double-buffered staging area, which leaves through cp.async.bulk stores;
-//   * with dropout, four more warps do nothing but generate the keep decisions:
-//     the Philox blocks of a tile are consecutive counters, so these warps fill
-//     the tile's mask bytes (one 8-byte store per block) into one of two mask
-//     buffers, from which one bulk store writes the mask to memory and the
-//     consumers read their keep bits.  The integer work of the generator thus
-//     runs in issue slots the consumers leave free, instead of in front of
-//     every row's arithmetic.  Without dropout the consumers write the (all
-//     ones) mask bytes themselves.
+//   * eight consumer warps take RPW rows each out of a stage, work on them in
+//     lockstep, hand the stage back, and write results and mask bytes into
+//     their own double-buffered staging area, which leaves through
+//     cp.async.bulk stores (one for the values, one for the mask per warp and tile).
 // The warps never wait on global memory: several tiles per SM are in flight in
-// each direction, whatever the arithmetic is doing.
+// each direction, whatever the arithmetic is doing.  (With dropout the kernel is
+// bound by instruction issue, not by memory: there the warp-per-row kernel,
+// which has the fewest instructions per element and the most resident warps, is
+// the faster one -- a variant of this kernel with dedicated generator warps
+// reached 4.0 TB/s against 5.0 TB/s -- so dropout never takes this path.)
 namespace stream {
 
 constexpr int WARPS = 8;            // consumer warps; warp WARPS is the producer
-constexpr int RNG_WARPS = 4;        // warps WARPS+1 .. : dropout decisions (kernels with dropout only)
+constexpr int THREADS = (WARPS + 1) * 32;
 constexpr int STAGES = 3;
-constexpr int MASK_BUFS = 2;        // tile-sized mask buffers filled by the generator warps
-template <bool DROP> struct Threads { static constexpr int value = (WARPS + 1 + (DROP ? RNG_WARPS : 0)) * 32; };
-enum : int { kWdStreamFull = 301, kWdStreamEmpty = 302, kWdMaskFull = 303, kWdMaskEmpty = 304 };
-__device__ __forceinline__ void rng_warps_sync() { asm volatile("bar.sync 1, %0;" ::"n"(RNG_WARPS * 32) : "memory"); }
-__device__ __forceinline__ uint2 lds8(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
+enum : int { kWdStreamFull = 301, kWdStreamEmpty = 302 };
 
 template <typename T, int CH> struct Cfg {
   static constexpr int ROW_BYTES_MAX = CH * 256 * (int)sizeof(T);
@@ -495,7 +594,6 @@ __device__ __forceinline__ void bulk_store(void* dst, uint32_t src, uint32_t byt
                : "memory");
 }
 __device__ __forceinline__ void bulk_wait_read_le1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
-__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ uint4 lds16(uint32_t addr) {
   uint4 v;
@@ -516,17 +614,11 @@ template <> __device__ __forceinline__ void unit_from_smem<float>(Unit<float>& u
   u.raw[1] = lds16(addr + 16);
 }
 
-// finish_unit_masked with shared-memory destinations; WRITE_MASK = false when
-// the mask bytes are already where they belong (written by the generator warps)
-template <typename T, bool WRITE_MASK>
+// One unit of a dropout-free row into the staging area: values, and eight mask bytes of 1.
+template <typename T>
 __device__ __forceinline__ void finish_unit_smem(const uint64_t (&e2)[4], uint64_t g2, uint32_t out_addr,
-                                                 uint32_t mask_addr, const uint32_t (&km)[4]) {
-  if constexpr (WRITE_MASK) {
-    uint2 mb;
-    mb.x = __byte_perm(km[0], km[1], 0x6420) & 0x01010101u;
-    mb.y = __byte_perm(km[2], km[3], 0x6420) & 0x01010101u;
-    sts8(mask_addr, mb);
-  }
+                                                 uint32_t mask_addr) {
+  sts8(mask_addr, make_uint2(0x01010101u, 0x01010101u));
   float2 y[4];
 #pragma unroll
   for (int k = 0; k < 4; ++k) y[k] = unpack2(mul2(e2[k], g2));
@@ -535,59 +627,39 @@ __device__ __forceinline__ void finish_unit_smem(const uint64_t (&e2)[4], uint64
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const __half2 h = __floats2half2_rn(y[k].x, y[k].y);
-      w[k] = *reinterpret_cast<const uint32_t*>(&h) & km[k];
+      w[k] = *reinterpret_cast<const uint32_t*>(&h);
     }
     sts16(out_addr, make_uint4(w[0], w[1], w[2], w[3]));
   } else {
-    uint32_t v[8];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      v[2 * k] = (km[k] & 0xFFFFu) ? __float_as_uint(y[k].x) : 0u;
-      v[2 * k + 1] = (km[k] >> 16) ? __float_as_uint(y[k].y) : 0u;
-    }
-    sts16(out_addr, make_uint4(v[0], v[1], v[2], v[3]));
-    sts16(out_addr + 16, make_uint4(v[4], v[5], v[6], v[7]));
+    sts16(out_addr, make_uint4(__float_as_uint(y[0].x), __float_as_uint(y[0].y), __float_as_uint(y[1].x),
+                               __float_as_uint(y[1].y)));
+    sts16(out_addr + 16, make_uint4(__float_as_uint(y[2].x), __float_as_uint(y[2].y), __float_as_uint(y[3].x),
+                                    __float_as_uint(y[3].y)));
   }
 }
 
-// Eight mask bytes (0 / 1) of one Philox block -> the four mask words of finish_unit_*.
-__device__ __forceinline__ void masks_from_bytes(uint2 mb, uint32_t (&km)[4]) {
-  const uint32_t t0 = mb.x * 0xFFu, t1 = mb.y * 0xFFu;     // bytes 0x00 / 0xFF
-  km[0] = __byte_perm(t0, 0u, 0x1100);
-  km[1] = __byte_perm(t0, 0u, 0x3322);
-  km[2] = __byte_perm(t1, 0u, 0x1100);
-  km[3] = __byte_perm(t1, 0u, 0x3322);
-}
-
-// dynamic shared memory:
-//   [STAGES x tile_bytes | WARPS x 2 x staging | DROP: MASK_BUFS x R*L mask bytes | barriers | abort flag]
-// staging of one consumer warp: RPW rows of output (+ RPW*L mask bytes without dropout)
-template <typename T, int CH, bool DROP, bool EXT>
-__global__ void __launch_bounds__(Threads<DROP>::value) softmax_stream_kernel(const SmParams p, int* status) {
+// dynamic shared memory: [STAGES x tile_bytes | WARPS x 2 x (RPW*row_bytes + RPW*L) | barriers | abort flag]
+template <typename T, int CH, bool EXT>
+__global__ void __launch_bounds__(THREADS) softmax_stream_kernel(const SmParams p, int* status) {
   using C = Cfg<T, CH>;
   constexpr int RPW = C::RPW, R = C::R;
   extern __shared__ __align__(128) uint8_t smem[];
   const int L = p.L;
   const uint32_t row_bytes = (uint32_t)L * (uint32_t)sizeof(T);
   const uint32_t tile_bytes = R * row_bytes;
-  const uint32_t tile_mask_bytes = R * (uint32_t)L;
-  const uint32_t wout_bytes = RPW * row_bytes, wmask_bytes = DROP ? 0u : RPW * (uint32_t)L;
+  const uint32_t wout_bytes = RPW * row_bytes, wmask_bytes = RPW * (uint32_t)L;
   const uint32_t wbuf_bytes = wout_bytes + wmask_bytes;            // one staging buffer of one warp
   const uint32_t s_in = smem_u32(smem);
   const uint32_t s_out = s_in + STAGES * tile_bytes;
-  const uint32_t s_mask = s_out + WARPS * 2 * wbuf_bytes;
-  const uint32_t bars = s_mask + (DROP ? MASK_BUFS * tile_mask_bytes : 0u);   // every size is a multiple of 16
+  const uint32_t bars = s_out + WARPS * 2 * wbuf_bytes;            // 8-byte aligned: every size is a multiple of 16
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  auto mfull_bar = [&](int b) { return bars + 8u * (2 * STAGES + b); };
-  auto mempty_bar = [&](int b) { return bars + 8u * (2 * STAGES + MASK_BUFS + b); };
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bars - s_in) + 8 * (2 * STAGES + 2 * MASK_BUFS));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + (bars - s_in) + 16 * STAGES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long num_tiles = (p.rows + R - 1) / R;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), WARPS); }
-    for (int b = 0; b < MASK_BUFS; ++b) { mbar_init(mfull_bar(b), 1); mbar_init(mempty_bar(b), WARPS); }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -608,56 +680,6 @@ __global__ void __launch_bounds__(Threads<DROP>::value) softmax_stream_kernel(co
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
-  } else if (warp > WARPS) {
-    // ------------------------------------------------- dropout decision generator
-    if constexpr (DROP) {
-      const int rt = threadIdx.x - (WARPS + 1) * 32;            // 0 .. RNG_WARPS*32-1
-      uint32_t it = 0;
-      bool ok = true;
-      for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
-        const uint32_t b = it % MASK_BUFS, parity = (it / MASK_BUFS) & 1u;
-        // the consumers have read the previous contents, and the copy engine has read them too
-        if (ok && !mbar_wait(mempty_bar(b), parity ^ 1u, abort_flag, status, kWdMaskEmpty)) ok = false;
-        if (rt == 0) bulk_wait_read_le1();
-        rng_warps_sync();
-        const long long row0 = tile * R;
-        const int nrows = (int)min((long long)R, p.rows - row0);
-        const int nblk = nrows * (L >> 3);
-        const unsigned long long blk0 = ((p.first_row + (unsigned long long)row0) * (unsigned long long)L) >> 3;
-        const uint32_t mb = s_mask + b * tile_mask_bytes;
-        if (ok) {
-          for (int i0 = rt; i0 < nblk; i0 += 4 * RNG_WARPS * 32) {
-            unsigned long long blk[4];
-            uint32_t o[4][4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) blk[q] = blk0 + (unsigned)(i0 + q * RNG_WARPS * 32);   // surplus blocks are discarded
-            philox_blocks<4>(blk, p.key, o);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int i = i0 + q * RNG_WARPS * 32;
-              if (i < nblk) {
-                uint32_t km[4];
-                masks_from_words<true>(p, o[q], km);
-                uint2 bytes;
-                bytes.x = __byte_perm(km[0], km[1], 0x6420) & 0x01010101u;
-                bytes.y = __byte_perm(km[2], km[3], 0x6420) & 0x01010101u;
-                sts8(mb + (uint32_t)i * 8u, bytes);
-              }
-            }
-          }
-        }
-        fence_proxy_async_smem();
-        rng_warps_sync();
-        if (rt == 0) {
-          if (ok && nrows > 0) {
-            bulk_store(p.mask + row0 * (long long)L, mb, (uint32_t)nrows * (uint32_t)L);
-            bulk_commit_group();
-          }
-          mbar_arrive(mfull_bar(b));
-        }
-      }
-      if (rt == 0) bulk_wait_all();
-    }
   } else {
     // --------------------------------------------------------------- consumers
     bool valid[CH];
@@ -665,8 +687,8 @@ __global__ void __launch_bounds__(Threads<DROP>::value) softmax_stream_kernel(co
     for (int c = 0; c < CH; ++c) valid[c] = (lane + 32 * c) * 8 < L;
     char* out = static_cast<char*>(p.out);
     const uint32_t my_out = s_out + warp * 2 * wbuf_bytes;
-    uint32_t stage = 0, phase = 0, buf = 0, it = 0;
-    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    uint32_t stage = 0, phase = 0, buf = 0;
+    for (long long tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const long long row0 = tile * R + warp * RPW;       // first of this warp's rows
       const int nrows = (int)max(0ll, min((long long)RPW, p.rows - row0));
       if (!mbar_wait(full_bar(stage), phase, abort_flag, status, kWdStreamFull)) break;
@@ -680,50 +702,40 @@ __global__ void __launch_bounds__(Threads<DROP>::value) softmax_stream_kernel(co
           else cur[r][c].fill_neg_inf();
         }
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar(stage));       // the rows are in registers: the stage may be refilled
-      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-
       // the staging buffer about to be written was handed to the copy engine two tiles ago
       if (lane == 0) bulk_wait_read_le1();
       __syncwarp();
-      const uint32_t ob = my_out + buf * wbuf_bytes, mbw = ob + wout_bytes;
-      const uint32_t mbuf = it % MASK_BUFS;
-      const uint32_t mtile = s_mask + mbuf * tile_mask_bytes + (uint32_t)(warp * RPW) * (uint32_t)L;
-      bool mask_ready = !DROP;
+      // all RPW rows in lockstep (rows past the end of the tensor are -inf filled and never stored)
+      uint64_t e2[RPW][CH][4], g2[RPW];
+      long long rws[RPW];
+#pragma unroll
+      for (int r = 0; r < RPW; ++r) rws[r] = min(row0 + r, p.rows - 1);
+      rows_exponentials<T, CH, EXT, RPW>(p, cur, rws, lane, e2, g2);
+      // Hand the stage back only now.  The copy engine refills it as soon as the
+      // eighth warp has arrived, and an arrive does not wait for shared-memory
+      // loads that are still in flight: issued right after the loads it let the
+      // refill overtake them (seen with FP32 rows, whose 32-byte lane pitch makes
+      // the loads replay).  Here every loaded word has been consumed -- by this
+      // lane's arithmetic and, through the reductions, by the whole warp.
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(stage));
+      if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+
+      const uint32_t ob = my_out + buf * wbuf_bytes, mb = ob + wout_bytes;
 #pragma unroll
       for (int r = 0; r < RPW; ++r) {
-        if (r < nrows) {
-          uint64_t e2[CH][4];
-          const uint64_t g2 = row_exponentials<T, CH, EXT>(p, cur[r], row0 + r, lane, e2);
-          if constexpr (DROP) {
-            if (!mask_ready) {       // as late as possible: the generator works while the exponentials are computed
-              mask_ready = mbar_wait(mfull_bar(mbuf), (it / MASK_BUFS) & 1u, abort_flag, status, kWdMaskFull);
-              if (!mask_ready) break;
-            }
-          }
 #pragma unroll
-          for (int c = 0; c < CH; ++c) {
-            if (valid[c]) {
-              uint32_t km[4];
-              if constexpr (DROP) masks_from_bytes(lds8(mtile + r * L + (lane + 32 * c) * 8), km);
-              else masks_from_words<false>(p, km, km);
-              finish_unit_smem<T, !DROP>(e2[c], g2, ob + r * row_bytes + (lane + 32 * c) * 8 * (uint32_t)sizeof(T),
-                                         mbw + r * L + (lane + 32 * c) * 8, km);
-            }
-          }
-        }
-      }
-      if constexpr (DROP) {
-        if (nrows > 0 && !mask_ready) break;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(mempty_bar(mbuf));     // this warp is done with the tile's mask buffer
+        for (int c = 0; c < CH; ++c)
+          if (valid[c])
+            finish_unit_smem<T>(e2[r][c], g2[r], ob + r * row_bytes + (lane + 32 * c) * 8 * (uint32_t)sizeof(T),
+                                mb + r * L + (lane + 32 * c) * 8);
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0 && nrows > 0) {
         bulk_store(out + row0 * (long long)row_bytes, ob, (uint32_t)nrows * row_bytes);
-        if constexpr (!DROP) bulk_store(p.mask + row0 * (long long)L, mbw, (uint32_t)nrows * (uint32_t)L);
+        bulk_store(p.mask + row0 * (long long)L, mb, (uint32_t)nrows * (uint32_t)L);
         bulk_commit_group();
       }
       buf ^= 1u;
@@ -1212,36 +1224,28 @@ void launch_warp(const SmParams& p, bool drop, bool ext, int sms, cudaStream_t s
   }
 }
 
-// Streaming kernel: needs whole 16-byte mask rows (L % 16 == 0, 16-byte aligned
-// mask pointer) and rows of at most 4 KB.
-template <typename T, int CH, bool DROP, bool EXT>
+// Streaming kernel (dropout-free only): needs whole 16-byte mask rows (L % 16 == 0,
+// 16-byte aligned mask pointer) and rows of at most 4 KB.
+template <typename T, int CH, bool EXT>
 void launch_stream_t(const SmParams& p, int sms, cudaStream_t stream) {
   using C = stream::Cfg<T, CH>;
   const size_t row_bytes = (size_t)p.L * sizeof(T);
-  constexpr int kThreads = stream::Threads<DROP>::value;
-  const size_t smem = stream::STAGES * C::R * row_bytes +
-                      (size_t)stream::WARPS * 2 * C::RPW * (row_bytes + (DROP ? 0 : p.L)) +
-                      (DROP ? (size_t)stream::MASK_BUFS * C::R * p.L : 0) +
-                      8 * (2 * stream::STAGES + 2 * stream::MASK_BUFS) + 16;
-  auto kern = stream::softmax_stream_kernel<T, CH, DROP, EXT>;
+  const size_t smem = stream::STAGES * C::R * row_bytes + (size_t)stream::WARPS * 2 * C::RPW * (row_bytes + p.L) +
+                      16 * stream::STAGES + 16;
+  auto kern = stream::softmax_stream_kernel<T, CH, EXT>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   int per_sm = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, kThreads, smem);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, stream::THREADS, smem);
   if (per_sm < 1) per_sm = 1;
   const long long tiles = (p.rows + C::R - 1) / C::R;
   const long long cap = (long long)sms * per_sm;
   const int grid = (int)(tiles < cap ? tiles : cap);
-  kern<<<grid, kThreads, smem, stream>>>(p, watchdog_word());
+  kern<<<grid, stream::THREADS, smem, stream>>>(p, watchdog_word());
 }
 template <typename T, int CH>
-void launch_stream(const SmParams& p, bool drop, bool ext, int sms, cudaStream_t stream) {
-  if (ext) {
-    if (drop) launch_stream_t<T, CH, true, true>(p, sms, stream);
-    else launch_stream_t<T, CH, false, true>(p, sms, stream);
-  } else {
-    if (drop) launch_stream_t<T, CH, true, false>(p, sms, stream);
-    else launch_stream_t<T, CH, false, false>(p, sms, stream);
-  }
+void launch_stream(const SmParams& p, bool ext, int sms, cudaStream_t stream) {
+  if (ext) launch_stream_t<T, CH, true>(p, sms, stream);
+  else launch_stream_t<T, CH, false>(p, sms, stream);
 }
 
 // 0 = choose by shape, 1 = warp kernel only, 2 = streaming kernel wherever it is eligible.
@@ -1258,7 +1262,8 @@ int softmax_form_override() {
 }
 
 template <typename T>
-bool stream_eligible(const SmParams& p) {
+bool stream_eligible(const SmParams& p, bool drop) {
+  if (drop) return false;    // bound by instruction issue: the warp-per-row kernel is faster there
   if (p.L % 16 != 0 || ((uintptr_t)p.mask & 15u) != 0) return false;
   if ((size_t)p.L * sizeof(T) > 4096) return false;
   const int form = softmax_form_override();
@@ -1282,11 +1287,11 @@ void launch_block(const SmParams& p, bool drop, bool ext, int warps, int sms, cu
 
 template <typename T>
 void dispatch(const SmParams& p, bool drop, bool ext, SoftmaxSchedule sch, int sms, cudaStream_t stream) {
-  if (sch.vec == 8 && sch.warps == 1 && stream_eligible<T>(p)) {
-    if (p.L <= 256) launch_stream<T, 1>(p, drop, ext, sms, stream);
-    else if (p.L <= 512) launch_stream<T, 2>(p, drop, ext, sms, stream);
-    else if (p.L <= 1024) launch_stream<T, 4>(p, drop, ext, sms, stream);
-    else launch_stream<T, 8>(p, drop, ext, sms, stream);
+  if (sch.vec == 8 && sch.warps == 1 && stream_eligible<T>(p, drop)) {
+    if (p.L <= 256) launch_stream<T, 1>(p, ext, sms, stream);
+    else if (p.L <= 512) launch_stream<T, 2>(p, ext, sms, stream);
+    else if (p.L <= 1024) launch_stream<T, 4>(p, ext, sms, stream);
+    else launch_stream<T, 8>(p, ext, sms, stream);
   } else if (sch.vec == 8 && sch.warps == 1) {
     if (p.L <= 256) launch_warp<T, 1>(p, drop, ext, sms, stream);
     else if (p.L <= 512) launch_warp<T, 2>(p, drop, ext, sms, stream);

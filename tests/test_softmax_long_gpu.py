@@ -56,7 +56,12 @@ def test_streaming_kernel_bit_exact(tf, oracle, dtype, rows, L, p):
             kept = mask[rb] == 1
             got = out[rb].astype(np.float64)[kept] * (1 - p)
             err = np.abs(base[:, kept] - got).sum(-1)
-            src.append((int(rb), int(np.argmin(err)), float(err.min())))
+            o = out[rb].astype(np.float64); w = want[rb].astype(np.float64)
+            nz = (o != 0) & (w != 0)
+            ratio = o[nz] / w[nz]
+            src.append((int(rb), int(np.argmin(err)), float(err.min()), "ratio min/max", float(ratio.min()), float(ratio.max()),
+                        "kept-but-zero", int(((o == 0) & (w != 0)).sum()), "dropped-but-nonzero", int(((o != 0) & (w == 0)).sum()),
+                        "first/last bad col", int(bad[bad[:, 0] == rb][0, 1]), int(bad[bad[:, 0] == rb][-1, 1])))
         raise AssertionError(f"{len(bad)} mismatches in rows {rows_bad.tolist()[:40]}; (row, best matching source row, "
                              f"L1 distance): {src}")
     assert np.all(out[11] == 0)
