@@ -44,7 +44,8 @@ M, K, N = 16384, 1024, 4096
 FLOP_PER_STEP = 2.0 * M * N * K
 NOMINAL = {"fp16_tflops": 2250.0, "int8_tops": 4500.0, "hbm_gbs": 8000.0}
 # DRAM bytes (read + write) of one launch, from one ncu capture of each kernel.
-NCU_TRAFFIC = {"gemm_fp16": 121.2e6, "gemm_int8": 440.1e6, "softmax_p0": 620.7e6, "softmax_p0.1": 618.1e6}
+NCU_TRAFFIC = {"gemm_fp16": 119.9e6, "gemm_int8": 440.1e6, "softmax_p0": 615.3e6, "softmax_p0.1": 617.6e6,
+               "softmax_long_p0": 1286.1e6, "gemm_fp32": 56.9e6}
 
 
 def measured_peaks():
@@ -626,7 +627,8 @@ def side_workloads(tf, L, dev, peaks, args):
             "metric": "fp32_gemm_bias_gelu_tflops", "value": 2.0 * M1 * N1 * K1 / (avg * 1e-3) / 1e12, "unit": "TFLOPS",
             "ms": avg, "ms_min": best, "config": {"workload": "fp32_gemm_bias_gelu_4096x768x3072"},
             "note": "tensor cores: each FP32 product rebuilt from three TF32 products (hi*hi + lo*hi + hi*lo), FP32 "
-                    "accumulation; includes the pass that splits A and B"}
+                    "accumulation; includes the pass that splits A and B",
+            "gemm_kernel_dram_traffic": NCU_TRAFFIC["gemm_fp32"]}
     except Exception as e:
         out["fp32_gemm_error"] = repr(e)
 
@@ -651,7 +653,8 @@ def side_workloads(tf, L, dev, peaks, args):
                                "kernel": "shared-memory resident row per CTA" if Lr == 8192 else
                                          "online (running maximum) sweep + write sweep: 7 B/element of DRAM traffic"},
                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                 "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes": rows * Lr * 5}}
+                                 "frac": gbs / peaks["hbm_gbs"], "algorithmic_bytes": rows * Lr * 5,
+                                 "traffic": NCU_TRAFFIC["softmax_long_p0"] if (Lr == 8192 and pd == 0.0) else None}}
             del xs, os_, ms_
             torch.cuda.empty_cache()
     except Exception as e:

@@ -61,7 +61,15 @@ TensorFuseStatus tensorfuse_fused_softmax_dropout(const TensorFuseTensor* input,
                                                   cudaStream_t stream);
 
 /* reference src/tensorfuse/tensorfuse.h:106,127; src/tensorfuse_c_api.cpp:288-329.
- * Argument validation only, as in the reference (which computes nothing). */
+ * The reference validates its arguments and computes nothing.  Here the same
+ * validation (same order, same codes) is followed by the computation:
+ *   attention   - query/key/value/output [batch, seq, hidden], FP16 or BF16,
+ *                 hidden / num_heads == 64: softmax(Q K^T / 8) V per head with
+ *                 dropout on the probabilities, one fused kernel;
+ *   transformer - a post-LayerNorm encoder layer (QKV projection, attention,
+ *                 output projection, residual + LayerNorm, FFN with GELU,
+ *                 residual + LayerNorm) on the caller's stream.
+ * Shapes or types outside those return TENSORFUSE_ERROR_UNSUPPORTED_OPERATION. */
 TensorFuseStatus tensorfuse_fused_multi_head_attention(const TensorFuseTensor* query,
                                                        const TensorFuseTensor* key,
                                                        const TensorFuseTensor* value,

@@ -369,11 +369,24 @@ def fused_gemm_bias_gelu(input, weight, bias, output=None, stream=None, *, scale
     return output
 
 
+def _check_cuda_out(op: str, t, shape, dtype, device):
+    """A caller-supplied CUDA result tensor is written through its raw pointer:
+    refuse anything but the exact dense tensor the operator is about to fill."""
+    if (not _is_torch(t) or not t.is_cuda or t.device != device or tuple(t.shape) != tuple(shape) or
+            not t.is_contiguous() or (dtype is not None and t.dtype != dtype)):
+        raise RuntimeError(f"{op} failed: " + get_error_string(Status.INVALID_TENSOR_SHAPE))
+
+
 def _gemm_torch_cuda(x, w, b, out, stream, scales, out_dtype, int8_mode):
     import torch
     x = x.contiguous(); w = w.contiguous(); b = b.contiguous()
+    if w.dim() != 2 or x.dim() < 1 or x.shape[-1] != w.shape[0] or b.numel() != w.shape[1] or \
+            w.device != x.device or b.device != x.device:
+        raise RuntimeError("fused_gemm_bias_gelu failed: " + get_error_string(Status.INVALID_TENSOR_SHAPE))
     K, N = w.shape
-    M = x.numel() // x.shape[-1]
+    M = x.numel() // max(1, x.shape[-1])
+    if out is not None:
+        _check_cuda_out("fused_gemm_bias_gelu", out, tuple(x.shape[:-1]) + (N,), out_dtype, x.device)
     in_dt = _torch_dt(x)
     s = _torch_stream(stream, x.device)
     with torch.cuda.device(x.device):
@@ -494,6 +507,8 @@ def fused_softmax_dropout_masked(input, scale=1.0, kv_lengths=None, dropout_prob
         output = torch.empty_like(x)
     if dropout_mask is None:
         dropout_mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    _check_cuda_out("fused_softmax_dropout_masked", output, x.shape, x.dtype, x.device)
+    _check_cuda_out("fused_softmax_dropout_masked", dropout_mask, x.shape, torch.uint8, x.device)
     lens_ptr = None
     if kv_lengths is not None:
         kv_lengths = torch.as_tensor(kv_lengths, dtype=torch.int32, device=x.device).contiguous()
@@ -522,6 +537,8 @@ def _softmax_torch_cuda(x, out, mask, p, stream, seed):
         out = torch.empty_like(x)
     if mask is None:
         mask = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    _check_cuda_out("fused_softmax_dropout", out, x.shape, x.dtype, x.device)
+    _check_cuda_out("fused_softmax_dropout", mask, x.shape, torch.uint8, x.device)
     s = _torch_stream(stream, x.device)
     dt = _torch_dt(x)
     with torch.cuda.device(x.device):
@@ -616,6 +633,7 @@ def fused_transformer_layer(input, weights, num_heads, dropout_prob=0.0, layer_n
     x = input.contiguous()
     if output is None:
         output = torch.empty_like(x)
+    _check_cuda_out("fused_transformer_layer", output, x.shape, x.dtype, x.device)
     dt = _torch_dt(x)
     params = TransformerParams()
     keep = []
@@ -649,7 +667,10 @@ def add_layernorm(x, residual, gamma, beta, eps=1e-12, output=None, stream=None)
     x = x.contiguous()
     if output is None:
         output = torch.empty_like(x)
+    _check_cuda_out("add_layernorm", output, x.shape, x.dtype, x.device)
     H = x.shape[-1]
+    if gamma.numel() != H or beta.numel() != H or (residual is not None and residual.shape != x.shape):
+        raise RuntimeError("add_layernorm failed: " + get_error_string(Status.INVALID_TENSOR_SHAPE))
     with torch.cuda.device(x.device):
         st = _auto_init(_L.tensorfuse_b200_add_layernorm, x.data_ptr(),
                         None if residual is None else residual.contiguous().data_ptr(), gamma.data_ptr(),

@@ -173,6 +173,8 @@ template <typename T> struct Unit;
 template <> struct Unit<__half> {
   uint4 raw;
   __device__ __forceinline__ void load(const __half* p) { raw = __ldcs(reinterpret_cast<const uint4*>(p)); }
+  // default caching: for data that is read again soon (second sweep of a long row, served by L2)
+  __device__ __forceinline__ void load_keep(const __half* p) { raw = __ldg(reinterpret_cast<const uint4*>(p)); }
   __device__ __forceinline__ void fill_neg_inf() { raw = make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u); }
   __device__ __forceinline__ void widen(float (&x)[8]) const {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -188,6 +190,10 @@ template <> struct Unit<float> {
   __device__ __forceinline__ void load(const float* p) {
     raw[0] = __ldcs(reinterpret_cast<const uint4*>(p));
     raw[1] = __ldcs(reinterpret_cast<const uint4*>(p) + 1);
+  }
+  __device__ __forceinline__ void load_keep(const float* p) {
+    raw[0] = __ldg(reinterpret_cast<const uint4*>(p));
+    raw[1] = __ldg(reinterpret_cast<const uint4*>(p) + 1);
   }
   __device__ __forceinline__ void fill_neg_inf() {
     raw[0] = raw[1] = make_uint4(0xFF800000u, 0xFF800000u, 0xFF800000u, 0xFF800000u);
@@ -1088,28 +1094,38 @@ __global__ void __launch_bounds__(THREADS) softmax_online_kernel(const SmParams 
     float mt = -INFINITY;
     uint64_t s2 = pack2(0.0f, 0.0f);
     uint64_t negc2 = pack2(0.0f, 0.0f);
-    for (int u = tid; u < units; u += THREADS) {
-      Unit<T> un; un.load(xr + u * 8);
-      float x[8]; un.widen(x);
-      adjust8<EXT>(x, u * 8, len, p.scale);
-      float mu = x[0];
+    // four units per thread and step: the loads are issued together, the units are
+    // then taken in ascending order (the order of the CPU restatement)
+    for (int u0 = tid; u0 < units; u0 += 4 * THREADS) {
+      Unit<T> un[4];
 #pragma unroll
-      for (int i = 1; i < 8; ++i) mu = fmaxf(mu, x[i]);
-      if (mu == -INFINITY) continue;                 // contributes nothing
-      if (mu > mt) {
-        const float negc = -__fmul_rn(mu, kLog2e);
-        if (mt != -INFINITY) {
-          const float t = fmaxf(__fmaf_rn(mt, kLog2e, negc), -127.0f);
-          const float2 f = unpack2(exp2_pair(pack2(t, t)));
-          s2 = mul2(s2, pack2(f.x, f.x));
+      for (int j = 0; j < 4; ++j)
+        if (u0 + j * THREADS < units) un[j].load_keep(xr + (size_t)(u0 + j * THREADS) * 8);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int u = u0 + j * THREADS;
+        if (u >= units) break;
+        float x[8]; un[j].widen(x);
+        adjust8<EXT>(x, u * 8, len, p.scale);
+        float mu = x[0];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) mu = fmaxf(mu, x[i]);
+        if (mu == -INFINITY) continue;                 // contributes nothing
+        if (mu > mt) {
+          const float negc = -__fmul_rn(mu, kLog2e);
+          if (mt != -INFINITY) {
+            const float t = fmaxf(__fmaf_rn(mt, kLog2e, negc), -127.0f);
+            const float2 f = unpack2(exp2_pair(pack2(t, t)));
+            s2 = mul2(s2, pack2(f.x, f.x));
+          }
+          mt = mu;
+          negc2 = pack2(negc, negc);
         }
-        mt = mu;
-        negc2 = pack2(negc, negc);
-      }
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 t = unpack2(fma2(pack2(x[2 * k], x[2 * k + 1]), log2e2, negc2));
-        s2 = add2(s2, exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f))));
+        for (int k = 0; k < 4; ++k) {
+          const float2 t = unpack2(fma2(pack2(x[2 * k], x[2 * k + 1]), log2e2, negc2));
+          s2 = add2(s2, exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f))));
+        }
       }
     }
     // row maximum
@@ -1144,18 +1160,39 @@ __global__ void __launch_bounds__(THREADS) softmax_online_kernel(const SmParams 
     const uint64_t rowc2 = pack2(negc, negc);
 
     const unsigned long long idx0 = (p.first_row + (unsigned long long)row) * (unsigned long long)L;
-    for (int u = tid; u < units; u += THREADS) {
-      Unit<T> un; un.load(xr + u * 8);
-      float x[8]; un.widen(x);
-      adjust8<EXT>(x, u * 8, len, p.scale);
-      uint64_t e2[4];
+    for (int u0 = tid; u0 < units; u0 += 4 * THREADS) {
+      Unit<T> un[4];
+      uint32_t km[4][4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 t = unpack2(fma2(pack2(x[2 * k], x[2 * k + 1]), log2e2, rowc2));
-        e2[k] = exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f)));
+      for (int j = 0; j < 4; ++j)
+        if (u0 + j * THREADS < units) un[j].load(xr + (size_t)(u0 + j * THREADS) * 8);
+      if (DROP) {
+        unsigned long long blk[4];
+        uint32_t o[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) blk[j] = (idx0 >> 3) + (unsigned)(u0 + j * THREADS);
+        philox_blocks<4>(blk, p.key, o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) masks_from_words<true>(p, o[j], km[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) masks_from_words<false>(p, km[j], km[j]);
       }
-      const long long off = row * L + (long long)u * 8;
-      finish_unit<T, DROP>(e2, g2, out + off, p.mask + off, p, (idx0 >> 3) + (unsigned)u);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int u = u0 + j * THREADS;
+        if (u >= units) break;
+        float x[8]; un[j].widen(x);
+        adjust8<EXT>(x, u * 8, len, p.scale);
+        uint64_t e2[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 t = unpack2(fma2(pack2(x[2 * k], x[2 * k + 1]), log2e2, rowc2));
+          e2[k] = exp2_pair(pack2(fmaxf(t.x, -127.0f), fmaxf(t.y, -127.0f)));
+        }
+        const long long off = row * L + (long long)u * 8;
+        finish_unit_masked<T, DROP>(e2, g2, out + off, p.mask + off, km[j]);
+      }
     }
   }
 }

@@ -143,6 +143,47 @@ def test_python_api_paths(tf, oracle):
         tf.fused_gemm_bias_gelu(x, w[:, :8], b)
 
 
+def test_cuda_tensor_results_are_validated_before_their_pointers_are_used(tf):
+    """Caller-supplied CUDA result tensors reach the library as raw pointers: a
+    wrong shape, type, layout or device must be refused in Python, not written through."""
+    x = torch.randn(2, 3, 8, 64, device="cuda", dtype=torch.float16)
+    good_out, good_mask = torch.empty_like(x), torch.empty(x.shape, dtype=torch.uint8, device="cuda")
+    bad = [(torch.empty(2, 3, 8, 32, device="cuda", dtype=torch.float16), good_mask),      # short rows
+           (torch.empty(x.shape, device="cuda", dtype=torch.float32), good_mask),          # wrong type
+           (torch.empty(2, 3, 64, 8, device="cuda", dtype=torch.float16).transpose(2, 3), good_mask),  # strided
+           (good_out, torch.empty(x.shape, dtype=torch.int32, device="cuda")),             # 4-byte mask
+           (good_out, torch.empty(x.shape, dtype=torch.uint8)),                            # host mask
+           (good_out, torch.empty(2, 3, 8, 16, dtype=torch.uint8, device="cuda"))]         # small mask
+    for seed in (None, 7):
+        for out, mask in bad:
+            with pytest.raises(RuntimeError, match="Invalid tensor shape"):
+                tf.fused_softmax_dropout(x, out, mask, 0.1, seed=seed)
+            with pytest.raises(RuntimeError, match="Invalid tensor shape"):
+                tf.fused_softmax_dropout_masked(x, 1.0, None, 0.1, out, mask, seed=seed)
+    o, m = tf.fused_softmax_dropout(x, good_out, good_mask, 0.0, seed=7)
+    torch.cuda.synchronize()
+    assert o is good_out and m is good_mask and bool((m == 1).all())
+    a = torch.randn(4, 16, 64, device="cuda", dtype=torch.float16)
+    w = torch.randn(64, 128, device="cuda", dtype=torch.float16)
+    b = torch.zeros(128, device="cuda", dtype=torch.float16)
+    for out in (torch.empty(4, 16, 64, device="cuda", dtype=torch.float16),
+                torch.empty(4, 128, 16, device="cuda", dtype=torch.float16).transpose(1, 2),
+                torch.empty(4, 16, 128, dtype=torch.float16)):
+        with pytest.raises(RuntimeError, match="Invalid tensor shape"):
+            tf.fused_gemm_bias_gelu(a, w, b, out)
+    with pytest.raises(RuntimeError, match="Invalid tensor shape"):
+        tf.fused_gemm_bias_gelu(a, w[:32], b)
+    q8 = torch.randint(-5, 5, (32, 64), device="cuda", dtype=torch.int8)
+    w8 = torch.randint(-5, 5, (64, 128), device="cuda", dtype=torch.int8)
+    with pytest.raises(RuntimeError, match="Invalid tensor shape"):
+        tf.fused_gemm_bias_gelu(q8, w8, b.float(), torch.empty(32, 64, device="cuda", dtype=torch.float16),
+                                scales=(0.1, 0.1))
+    with pytest.raises(RuntimeError, match="Invalid tensor shape"):
+        tf.add_layernorm(a, None, torch.ones(64, device="cuda", dtype=torch.float16),
+                         torch.zeros(64, device="cuda", dtype=torch.float16), output=torch.empty(4, 16, 32, device="cuda",
+                                                                                                  dtype=torch.float16))
+
+
 def test_config1_full_size_through_the_struct_entry(tf, oracle):
     """Benchmark configuration 1 exactly: X[32,128,768] ~ N(0,1), W[768,3072] ~ N(0,1/768),
     b ~ N(0, 0.02^2), seed 0, FP32, 3-D tensors through tensorfuse_fused_gemm_bias_gelu; the
