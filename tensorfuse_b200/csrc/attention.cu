@@ -136,8 +136,10 @@ LaunchResult run_simt(const AttnArgs& a, float scale, cudaStream_t stream) {
 // of one head: 128 rows of 128 bytes, 128-byte swizzle.
 struct Map4Key {
   const void* base; int seq, heads, batch; long long ld, hs, bs;
+  int box_rows = 128;     // sequence positions per box: 128 for loads, 32 for a warp's output rows
   bool operator==(const Map4Key& o) const {
-    return base == o.base && seq == o.seq && heads == o.heads && batch == o.batch && ld == o.ld && hs == o.hs && bs == o.bs;
+    return base == o.base && seq == o.seq && heads == o.heads && batch == o.batch && ld == o.ld && hs == o.hs &&
+           bs == o.bs && box_rows == o.box_rows;
   }
 };
 bool make_map4(CUtensorMap* m, const Map4Key& k) {
@@ -145,7 +147,7 @@ bool make_map4(CUtensorMap* m, const Map4Key& k) {
   if (!fn) return false;
   const cuuint64_t gdim[4] = {(cuuint64_t)attn::HD, (cuuint64_t)k.seq, (cuuint64_t)k.heads, (cuuint64_t)k.batch};
   const cuuint64_t gstride[3] = {(cuuint64_t)k.ld * 2, (cuuint64_t)k.hs * 2, (cuuint64_t)k.bs * 2};
-  const cuuint32_t box[4] = {(cuuint32_t)attn::HD, 128u, 1u, 1u};
+  const cuuint32_t box[4] = {(cuuint32_t)attn::HD, (cuuint32_t)k.box_rows, 1u, 1u};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(k.base), gdim, gstride, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -192,7 +194,7 @@ LaunchResult run_tc(const AttnArgs& a, float scale, cudaStream_t stream) {
   if (!cached_map4(Map4Key{a.q, a.seq_q, a.heads, a.batch, a.ld_q, a.hs_q, a.bs_q}, &mq) ||
       !cached_map4(Map4Key{a.k, a.seq_kv, a.heads, a.batch, a.ld_k, a.hs_k, a.bs_k}, &mk) ||
       !cached_map4(Map4Key{a.v, a.seq_kv, a.heads, a.batch, a.ld_v, a.hs_v, a.bs_v}, &mv) ||
-      !cached_map4(Map4Key{a.out, a.seq_q, a.heads, a.batch, a.ld_o, a.hs_o, a.bs_o}, &mo))
+      !cached_map4(Map4Key{a.out, a.seq_q, a.heads, a.batch, a.ld_o, a.hs_o, a.bs_o, 32}, &mo))
     return kLaunchFailed;
   Params p;
   p.batch = a.batch; p.heads = a.heads; p.seq_q = a.seq_q; p.seq_kv = a.seq_kv;

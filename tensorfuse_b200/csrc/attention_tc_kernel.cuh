@@ -5,13 +5,13 @@
 // operator and leaves it empty: reference src/tensorfuse_c_api.cpp:288-311.)
 //
 // A work item is 128 query rows of one head; its keys are walked in blocks of
-// 128.  The kernel is persistent: two CTAs per SM (96 KB of shared memory, 256
+// 128.  The kernel is persistent: two CTAs per SM (112 KB of shared memory, 256
 // TMEM columns each) take work items round-robin, so TMEM allocation, barrier
 // set-up and descriptor fetches happen once, the next item's Q, K, V arrive and
 // its first scores are computed while the current item's output rows are
 // normalised and stored, and one CTA's softmax arithmetic overlaps the other's
 // tensor-core work.
-//   warp 0, one lane : TMA producer.  Q once; K and V blocks into a 2-deep ring
+//   warp 0, one lane : TMA producer.  Q of this and of the next item (two stages); K and V blocks into a 2-deep ring
 //                      of 128-byte-swizzled boxes (4-D tensor maps: any batch /
 //                      sequence / head strides, zero fill past the sequence end).
 //   warp 1, one lane : tcgen05.mma issuer.  S = Q K_j^T (M 128, N 128, K 64: both
@@ -30,8 +30,8 @@
 //                      running maximum moves, the same thread rescales its O row
 //                      in TMEM (tcgen05.ld / st) before releasing P to the MMA
 //                      issuer.  The final O row is divided by the row sum, scaled
-//                      by 1/(1-p), converted, staged in a 16 KB box and stored
-//                      through TMA.
+//                      by 1/(1-p), converted and staged; each warp stores its own 32
+//                      rows through TMA, so the warps never wait for one another.
 // Every mbarrier wait is bounded (ptx.cuh): an expired wait raises the CTA abort
 // flag, records a code in the watchdog word, and all roles fall through to the
 // tear-down that frees TMEM.
@@ -51,24 +51,26 @@ constexpr int BQ = 128;    // query rows per CTA
 constexpr int BKV = 128;   // keys per block
 constexpr int HD = 64;     // head width
 constexpr int KV_STAGES = 2;
+constexpr float kRescaleSlack = 8.0f;   // log2 of the largest unnormalised probability kept without rescaling
 constexpr int TILE_BYTES = 128 * 128;          // 128 rows of 64 FP16
 constexpr int NUM_THREADS = 192;
 constexpr int SOFTMAX_THREADS = 128;
 constexpr int TMEM_COLS = 256;                 // S: 0..127, O: 128..191, P (FP16 pairs): 192..255
+constexpr int Q_STAGES = 2;                    // the next item's query rows arrive during the current item
 constexpr int OFF_Q = 0;
-constexpr int OFF_K = OFF_Q + TILE_BYTES;
+constexpr int OFF_K = OFF_Q + Q_STAGES * TILE_BYTES;
 constexpr int OFF_V = OFF_K + KV_STAGES * TILE_BYTES;
 constexpr int OFF_P = OFF_V + KV_STAGES * TILE_BYTES;   // staging box of the output rows
 constexpr int OFF_BAR = OFF_P + TILE_BYTES;
-// barriers: q_full, q_empty, k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_free, p_full, o_done
-constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 5;   // + the softmax warps' own rendezvous
+// barriers: q_full[2], q_empty[2], k_full[2], v_full[2], k_empty[2], v_empty[2], s_full, s_free, p_full, o_done
+constexpr int NUM_BARS = 2 * Q_STAGES + 4 * KV_STAGES + 4;
 constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16;
 static_assert(2 * (SMEM_BYTES + 1024) <= 233472, "two CTAs per SM");
 
 // watchdog codes of this kernel
 enum : int { kWdQ = 201, kWdKFull = 202, kWdVFull = 203, kWdKEmpty = 204, kWdVEmpty = 205, kWdSFull = 206,
-             kWdSFree = 207, kWdPFull = 208, kWdODone = 209, kWdAlign = 210, kWdSync = 211 };
+             kWdSFree = 207, kWdPFull = 208, kWdODone = 209, kWdAlign = 210 };
 
 struct Params {
   int batch, heads, seq_q, seq_kv;
@@ -127,7 +129,7 @@ __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
 template <bool DROP, bool BF16>
 __global__ void __launch_bounds__(NUM_THREADS, 2)
 attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO32,
                     const __grid_constant__ Params p, int* status) {
   extern __shared__ __align__(1024) uint8_t smem[];
   if ((smem_u32(smem) & 1023u) != 0u) {
@@ -137,14 +139,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t sQ = smem_u32(smem + OFF_Q), sK = smem_u32(smem + OFF_K), sV = smem_u32(smem + OFF_V),
                  sP = smem_u32(smem + OFF_P);
   const uint32_t bars = smem_u32(smem + OFF_BAR);
-  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8u;
-  auto k_full = [&](int s) { return bars + 8u * (2 + s); };
-  auto v_full = [&](int s) { return bars + 8u * (2 + KV_STAGES + s); };
-  auto k_empty = [&](int s) { return bars + 8u * (2 + 2 * KV_STAGES + s); };
-  auto v_empty = [&](int s) { return bars + 8u * (2 + 3 * KV_STAGES + s); };
-  const uint32_t bar_s_full = bars + 8u * (2 + 4 * KV_STAGES);
+  auto q_full = [&](uint32_t s) { return bars + 8u * s; };
+  auto q_empty = [&](uint32_t s) { return bars + 8u * (Q_STAGES + s); };
+  constexpr int KB = 2 * Q_STAGES;
+  auto k_full = [&](int s) { return bars + 8u * (KB + s); };
+  auto v_full = [&](int s) { return bars + 8u * (KB + KV_STAGES + s); };
+  auto k_empty = [&](int s) { return bars + 8u * (KB + 2 * KV_STAGES + s); };
+  auto v_empty = [&](int s) { return bars + 8u * (KB + 3 * KV_STAGES + s); };
+  const uint32_t bar_s_full = bars + 8u * (KB + 4 * KV_STAGES);
   const uint32_t bar_s_free = bar_s_full + 8u, bar_p_full = bar_s_full + 16u, bar_o_done = bar_s_full + 24u;
-  const uint32_t bar_sm_sync = bar_s_full + 32u;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
 
@@ -162,8 +165,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   };
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_q_full, 1);
-    mbar_init(bar_q_empty, 1);
+    for (int s = 0; s < Q_STAGES; ++s) { mbar_init(q_full(s), 1); mbar_init(q_empty(s), 1); }
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(k_full(s), 1); mbar_init(v_full(s), 1); mbar_init(k_empty(s), 1); mbar_init(v_empty(s), 1);
     }
@@ -171,10 +173,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(bar_s_free, SOFTMAX_THREADS);
     mbar_init(bar_p_full, SOFTMAX_THREADS);
     mbar_init(bar_o_done, 1);
-    mbar_init(bar_sm_sync, SOFTMAX_THREADS);
     *abort_flag = 0;
     mbar_fence_init();
-    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO);
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmO32);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
@@ -198,9 +199,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tile_coords(t, q0, h, b, kv_len);
         const int nblk = (kv_len + BKV - 1) / BKV;
         if (nblk == 0) continue;
-        if (!mbar_wait(bar_q_empty, (wt & 1u) ^ 1u, abort_flag, status, kWdQ)) break;
-        mbar_arrive_expect_tx(bar_q_full, TILE_BYTES);
-        tma_load_4d(sQ, &tmQ, bar_q_full, 0, q0, h, b);
+        const uint32_t qs = wt % Q_STAGES, qph = (wt / Q_STAGES) & 1u;
+        if (!mbar_wait(q_empty(qs), qph ^ 1u, abort_flag, status, kWdQ)) break;
+        mbar_arrive_expect_tx(q_full(qs), TILE_BYTES);
+        tma_load_4d(sQ + qs * TILE_BYTES, &tmQ, q_full(qs), 0, q0, h, b);
         ++wt;
         for (int j = 0; j < nblk; ++j, ++g) {
           const int s = g % KV_STAGES;
@@ -222,7 +224,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       constexpr uint32_t IDESC_O = make_idesc_major(1u, FMT, 0u, 1u, BQ, HD);    // P K-major, V MN-major
       const uint32_t tS = tmem_base, tO = tmem_base + 128, tP = tmem_base + 192;
       // S = Q K^T of key block number gi (counted over the whole CTA)
-      auto issue_s = [&](uint32_t gi, bool last_of_item) -> bool {
+      // `qi` = number of the item (with key blocks) the block belongs to: selects the Q stage
+      auto issue_s = [&](uint32_t gi, uint32_t qi, bool last_of_item) -> bool {
+        const uint32_t qs = qi % Q_STAGES;
         const int s = gi % KV_STAGES;
         const uint32_t ph = (gi / KV_STAGES) & 1u;
         if (!mbar_wait(k_full(s), ph, abort_flag, status, kWdKFull)) return false;
@@ -230,11 +234,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk)
-          tc_mma_f16(tS, make_smem_desc(sQ + kk * 32, 16, 1024), make_smem_desc(sK + s * TILE_BYTES + kk * 32, 16, 1024),
-                     IDESC_S, kk != 0 ? 1u : 0u);
+          tc_mma_f16(tS, make_smem_desc(sQ + qs * TILE_BYTES + kk * 32, 16, 1024),
+                     make_smem_desc(sK + s * TILE_BYTES + kk * 32, 16, 1024), IDESC_S, kk != 0 ? 1u : 0u);
         tc_commit(bar_s_full);
         tc_commit(k_empty(s));
-        if (last_of_item) tc_commit(bar_q_empty);     // Q may be replaced by the next item's rows
+        if (last_of_item) tc_commit(q_empty(qs));     // this Q stage may take another item's rows
         return true;
       };
       uint32_t wt = 0, g = 0;
@@ -251,24 +255,25 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         return false;
       };
       bool have = next_item();
+      // wt = items started so far; the current item is number wt - 1
       if (have) {
-        ok = mbar_wait(bar_q_full, wt & 1u, abort_flag, status, kWdQ);
+        ok = mbar_wait(q_full(wt % Q_STAGES), (wt / Q_STAGES) & 1u, abort_flag, status, kWdQ);
         ++wt;
-        ok = ok && issue_s(g, nblk == 1);
+        ok = ok && issue_s(g, wt - 1, nblk == 1);
       }
       while (have && ok) {
         const int nb = nblk;
         for (int j = 0; j < nb && ok; ++j, ++g) {
           if (j + 1 < nb) {
-            if (!issue_s(g + 1, j + 2 == nb)) { ok = false; break; }
+            if (!issue_s(g + 1, wt - 1, j + 2 == nb)) { ok = false; break; }
           } else {
             // the scores of the next item's first block go out before this item's last P V
             t += gridDim.x;
             have = next_item();
             if (have) {
-              if (!mbar_wait(bar_q_full, wt & 1u, abort_flag, status, kWdQ)) { ok = false; break; }
+              if (!mbar_wait(q_full(wt % Q_STAGES), (wt / Q_STAGES) & 1u, abort_flag, status, kWdQ)) { ok = false; break; }
               ++wt;
-              if (!issue_s(g + 1, nblk == 1)) { ok = false; break; }
+              if (!issue_s(g + 1, wt - 1, nblk == 1)) { ok = false; break; }
             }
           }
           const int s = g % KV_STAGES;
@@ -301,23 +306,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     auto wait_warp = [&](uint32_t bar, uint32_t parity, int code) {
       return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, abort_flag, status, code)) != 0;
     };
-    // Rendezvous of the four softmax warps on an mbarrier, bounded like every
-    // other wait (a named barrier would hang the CTA if one warp had given up).
-    uint32_t sync_phase = 0;
-    auto softmax_sync = [&]() {
-      mbar_arrive(bar_sm_sync);
-      const bool w = wait_warp(bar_sm_sync, sync_phase, kWdSync);
-      sync_phase ^= 1u;
-      return w;
-    };
-    // the staging box is written again only after the previous store has read it
+    // Each warp stages and stores its own 32 output rows (a 4 KB slice of the
+    // box): the slice is written again only after the warp's previous store has read it.
+    const uint32_t sPw = sP + qtr * (32 * 128);
     auto staging_ready = [&]() {
       if (store_pending) {
-        if (threadIdx.x == 64) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         store_pending = false;
-        return softmax_sync();
+        __syncwarp();
       }
-      return true;
     };
     // Pass 1: maximum of the 128 scores of the row.  TAIL: the block holds fewer
     // than 128 real keys (columns >= valid are zero-filled, not scores).
@@ -424,8 +421,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int valid = kv_len - j * BKV;     // columns of this block that are real keys
         const bool tail = valid < BKV;
         const float mx = tail ? pass1(TrueT{}, valid) : pass1(FalseT{}, valid);
-        const float m_new = fmaxf(m_run, mx * sl2);
-        const float alpha = ex2_approx(m_run - m_new);     // 0 on the first block
+        // The reference point of the exponentials moves only when the block maximum
+        // exceeds it by more than 2^8: probabilities up to 256 are as exact in 16 bits
+        // as probabilities up to 1, the row sum is taken against the same reference,
+        // and the O row is then rescaled for the first block of an item and almost
+        // never again.
+        const float mb = mx * sl2;
+        const float m_new = mb > m_run + kRescaleSlack ? mb : m_run;
+        const float alpha = m_new == m_run ? 1.0f : ex2_approx(m_run - m_new);     // 0 on the first block
         // P and O are still in use by the previous block's second MMA
         if (j > 0 && !wait_warp(bar_o_done, (g - 1) & 1u, kWdODone)) { ok = false; break; }
         tc_fence_after();
@@ -451,7 +454,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (ok && nblk > 0) ok = wait_warp(bar_o_done, (g - 1) & 1u, kWdODone);
       if (!ok) break;
       tc_fence_after();
-      if (!staging_ready()) break;
+      staging_ready();
       const float inv = nblk > 0 && l_run > 0.0f ? p.keep_scale / l_run : 0.0f;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
@@ -475,14 +478,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       fence_proxy_async_smem();
       tc_fence_before();                       // the O reads above precede the next item's first P V
-      if (!softmax_sync()) break;
-      if (threadIdx.x == 64) {
-        tma_store_4d(&tmO, sP, 0, q0, h, b);
+      __syncwarp();
+      if (lane == 0 && q0 + qtr * 32 < p.seq_q) {
+        tma_store_4d(&tmO32, sPw, 0, q0 + qtr * 32, h, b);
         bulk_commit_group();
       }
       store_pending = true;
     }
-    if (threadIdx.x == 64) bulk_wait_group0();
+    if (lane == 0) bulk_wait_group0();
   }
 
   // ------------------------------------------------------------------ tear-down
