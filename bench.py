@@ -680,7 +680,7 @@ def side_workloads(tf, L, dev, peaks, args):
                 "metric": "attention_forward_tflops", "value": flop / (avg * 1e-3) / 1e12, "unit": "TFLOPS",
                 "ms": avg, "ms_min": best,
                 "config": {"workload": "attention_32x16x512x64", "dropout": pd, "flop": "4*B*H*S*S*d"},
-                "note": "bounded by the exponent unit (16 ex2 per clock and SM), not by the tensor cores"}
+                "note": "bounded by the serial scores -> softmax -> P V chain of each CTA (tensor pipe ~25 % active), not by the tensor cores"}
     except Exception as e:
         out["fused_attention_error"] = repr(e)
 

@@ -77,6 +77,37 @@ def test_layer_dropout_uses_the_library_seed_source(tf, oracle):
     check_watchdog()
 
 
+def test_layer_with_registered_projection_weights(tf):
+    """Registering the query/key/value weights lets the layer build its fused
+    [hidden, 3 x hidden] projection weight once.  The result must be bit-identical
+    to the unregistered call; after the weights change, the stale fused copy is
+    used until invalidate_weights is called (the contract of registration), and
+    the fresh one afterwards."""
+    B, S, H, heads, F = 2, 128, 256, 4, 512
+    w = layer_weights(H, F, np.float16, seed=5)
+    x = dev(np.random.default_rng(6).standard_normal((B, S, H)).astype(np.float16))
+    dw = {k: dev(v) for k, v in w.items()}
+    plain = host(tf.fused_transformer_layer(x, dw, heads, 0.0, 1e-5))
+    tf.register_weights(dw["query_weight"], dw["key_weight"], dw["value_weight"])
+    try:
+        first = host(tf.fused_transformer_layer(x, dw, heads, 0.0, 1e-5))      # builds the fused weight
+        again = host(tf.fused_transformer_layer(x, dw, heads, 0.0, 1e-5))      # reuses it
+        assert np.array_equal(first, plain) and np.array_equal(again, plain)
+        original = dw["query_weight"].clone()
+        dw["query_weight"].mul_(0.5)                                           # weights change behind the cache
+        torch.cuda.synchronize()
+        stale = host(tf.fused_transformer_layer(x, dw, heads, 0.0, 1e-5))
+        assert np.array_equal(stale, plain)
+    finally:
+        tf.invalidate_weights()
+    fresh = host(tf.fused_transformer_layer(x, dw, heads, 0.0, 1e-5))
+    assert not np.array_equal(fresh, plain)
+    dw["query_weight"].copy_(original)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(tf.fused_transformer_layer(x, dw, heads, 0.0, 1e-5)), plain)
+    check_watchdog()
+
+
 def test_layer_validation(tf):
     import tensorfuse_b200 as t
     H, F = 64, 128
