@@ -635,7 +635,7 @@ def side_workloads(tf, L, dev, peaks, args):
     # --- softmax + dropout on long rows: shared-memory resident rows and the online kernel
     try:
         for tag, rows, Lr in (("softmax_dropout_fp16_rows8192", 4 * 16 * 512, 8192),
-                              ("softmax_dropout_fp16_rows1Mi_online", 192, 1 << 20)):
+                              ("softmax_dropout_fp16_rows1Mi_online", 296, 1 << 20)):   # two rows per SM
             sets = 2 if tag.endswith("8192") else 3       # > 126 MB L2 in every case
             xs = [torch.randn((rows, Lr), device=dev).half() for _ in range(sets)]
             os_ = [torch.empty_like(x) for x in xs]
@@ -753,7 +753,7 @@ def run_only(args):
         work, unit = 2.0 * M1 * N1 * K1 / 1e12, "TFLOPS"
     elif args.only in ("softmax_long", "softmax_long_p0", "softmax_online"):
         # [4,16,512,8192] FP16 (shared-memory resident rows) or 256 rows of 1 Mi elements (online kernel)
-        rows, Lr = (4 * 16 * 512, 8192) if args.only != "softmax_online" else (256, 1 << 20)
+        rows, Lr = (4 * 16 * 512, 8192) if args.only != "softmax_online" else (296, 1 << 20)
         x = (torch.randn((rows, Lr), device=dev)).half(); o = torch.empty_like(x)
         m = torch.empty((rows, Lr), dtype=torch.uint8, device=dev)
         p = 0.0 if args.only == "softmax_long_p0" else 0.1
