@@ -59,7 +59,10 @@ class Runtime {
   // Concatenated copy of three registered device weight matrices (and biases),
   // kept per device until the registration of any of them is invalidated.
   // Returns null when it has to be (re)built: the caller fills `*slot` then.
-  struct FusedQkv { void* w = nullptr; void* b = nullptr; size_t w_bytes = 0, b_bytes = 0; };
+  struct FusedQkv {
+    std::mutex mu;       // held while the copy is (re)built: two first calls may arrive together
+    void* w = nullptr; void* b = nullptr; size_t w_bytes = 0, b_bytes = 0;
+  };
   FusedQkv* fused_qkv_slot(int device, const void* wq, const void* wk, const void* wv, bool* fresh);
   void register_weights(const void* host_ptr, size_t bytes);
   void invalidate_weights(const void* host_ptr);   // null: all of them

@@ -8,12 +8,15 @@
 // weights only.  The reference declares the entry point and the parameter block
 // (src/tensorfuse/tensorfuse.h:116-133, src/tensorfuse/types.h:153-185) and
 // returns success without touching the output (src/tensorfuse_c_api.cpp:313-329).
-// Workspace (4 x [tokens, hidden] + [tokens, ffn] + the concatenated weight) comes from the stream-ordered
-// allocator and is returned to it on the same stream, so the call stays
-// asynchronous and calls on different streams do not share buffers; the first
-// call on a device raises the release threshold of that device's default pool
-// so that the workspace stays cached between calls.
+// Workspace (4 x [tokens, hidden] + [tokens, ffn] + the concatenated weight) comes
+// from a stream-ordered memory pool that the library owns (one per device, kept
+// until shutdown) and is returned to it on the same stream, so the call stays
+// asynchronous, calls on different streams do not share buffers, and the
+// process's default pool is left alone.  When the three projection weights are
+// registered as immutable the concatenated weight is built once and kept.
 #include <cuda_runtime.h>
+
+#include <mutex>
 
 #include "kernels.h"
 #include "runtime.h"
@@ -139,8 +142,13 @@ extern "C" TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseT
   if (!p->use_bias) cuda_step(cudaMemsetAsync(bcat, 0, bcat_bytes, stream));
   cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
   cudaStreamIsCapturing(stream, &capturing);
+  std::unique_lock<std::mutex> slot_lock;
+  if (slot != nullptr) slot_lock = std::unique_lock<std::mutex>(slot->mu);
   const bool must_build = slot != nullptr && (fresh || slot->w_bytes != wcat_bytes || slot->b_bytes != bcat_bytes);
-  if (must_build && capturing != cudaStreamCaptureStatusNone) slot = nullptr;   // building synchronises: not inside a capture
+  if (must_build && capturing != cudaStreamCaptureStatusNone) {   // building synchronises: not inside a capture
+    slot_lock.unlock();
+    slot = nullptr;
+  }
   if (slot != nullptr && p->use_bias) {
     if (must_build) {
       if (slot->w) cudaFree(slot->w);
@@ -158,6 +166,7 @@ extern "C" TensorFuseStatus tensorfuse_fused_transformer_layer(const TensorFuseT
     }
     if (slot->w != nullptr) { w_qkv = static_cast<const char*>(slot->w); b_qkv = static_cast<const char*>(slot->b); }
   }
+  if (slot_lock.owns_lock()) slot_lock.unlock();
   if (w_qkv == wcat) concatenate(wcat, bcat);
   step(gemm(input->data, w_qkv, b_qkv, qkv, M, 3 * H, H, kdt, kEpiLinear, beta, stream));
   if (r == kOk) {
