@@ -234,20 +234,17 @@ LaunchResult run_tf32x3(const GemmArgs& a, cudaStream_t stream) {
   float* bh = reinterpret_cast<float*>(ws + 2 * a_bytes);
   float* bl = reinterpret_cast<float*>(ws + 2 * a_bytes + b_bytes);
   const int sms = sm_count(dev);
-  auto split = [&](const void* x, float* hi, float* lo, size_t elems) {
-    const long long n4 = (long long)(elems / 4);
-    const long long want = (n4 + 255) / 256;
-    const int grid = (int)(want < (long long)sms * 8 ? want : (long long)sms * 8);
-    split_tf32_kernel<<<grid > 0 ? grid : 1, 256, 0, stream>>>(static_cast<const float4*>(x), reinterpret_cast<float4*>(hi),
-                                                             reinterpret_cast<float4*>(lo), n4);
-  };
-  split(a.A, ah, al, a_elems);
   {
+    const long long n4 = (long long)(a_elems / 4);
+    const long long want_a = (n4 + 255) / 256;
+    const int blocks_a = (int)(want_a < (long long)sms * 6 ? (want_a > 0 ? want_a : 1) : (long long)sms * 6);
     const long long tiles = (long long)((a.N + 31) / 32) * ((a.K + 31) / 32);
-    const int grid = (int)(tiles < (long long)sms * 8 ? tiles : (long long)sms * 8);
-    split_transpose_tf32_kernel<<<grid, dim3(32, 8), 0, stream>>>(static_cast<const float*>(a.B), bh, bl, a.K, a.N);
+    const int blocks_b = (int)(tiles < (long long)sms * 6 ? (tiles > 0 ? tiles : 1) : (long long)sms * 6);
+    split_operands_kernel<<<blocks_a + blocks_b, 256, 0, stream>>>(static_cast<const float4*>(a.A), reinterpret_cast<float4*>(ah),
+                                                                   reinterpret_cast<float4*>(al), n4, blocks_a,
+                                                                   static_cast<const float*>(a.B), bh, bl, a.K, a.N);
   }
-  count_launch(2);
+  count_launch(1);
   LaunchResult res = kOk;
   CUtensorMap mah, mal, mbh, mbl, mc;
   if (!cached_map(MapKey{ah, 4, a.M, a.K, TBM}, &mah) || !cached_map(MapKey{al, 4, a.M, a.K, TBM}, &mal) ||
@@ -258,10 +255,24 @@ LaunchResult run_tf32x3(const GemmArgs& a, cudaStream_t stream) {
     const int tiles = ((a.M + 2 * TBM - 1) / (2 * TBM)) * ((a.N + TBN - 1) / TBN);
     const int pairs = tiles < max_clusters[dev] ? tiles : max_clusters[dev];
     EpiParams ep{a.alpha, a.beta, a.scale, a.scale_a_dev, a.scale_b_dev, nullptr};
-    kernel<<<2 * pairs, NUM_THREADS, X_SMEM_BYTES, stream>>>(mah, mal, mbh, mbl, mc, a.bias, a.bias_dtype, a.M, a.N, a.K,
-                                                            ep, watchdog_word());
+    // programmatic dependent launch: the GEMM's set-up overlaps the tail of the split kernel
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)pairs);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = X_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr; cfg.numAttrs = 1;
+    const void* bias_p = a.bias;
+    int bias_dt = a.bias_dtype, M_ = a.M, N_ = a.N, K_ = a.K;
+    int* wd = watchdog_word();
+    if (cudaLaunchKernelEx(&cfg, kernel, mah, mal, mbh, mbl, mc, bias_p, bias_dt, M_, N_, K_, ep, wd) != cudaSuccess) {
+      cudaGetLastError();
+      res = kLaunchFailed;
+    }
     count_launch();
-    if (cudaGetLastError() != cudaSuccess) res = kLaunchFailed;
   }
   cudaFreeAsync(ws, stream);
   return res;

@@ -1,8 +1,8 @@
 // gemm_tf32x3_kernel.cuh -- FP32 GEMM + bias + GELU on the tensor cores.
 //
 // An FP32 product is rebuilt from three TF32 tensor-core products: every operand
-// x is split into hi = tf32(x) and lo = tf32(x - hi) (split_tf32_kernel, one
-// pass over A and B into scratch planes) and
+// x is split into hi = tf32(x) and lo = tf32(x - hi) (split_operands_kernel, one
+// launch, one pass over A and B into scratch planes) and
 //     A*B  ~=  A_hi*B_hi + A_lo*B_hi + A_hi*B_lo          (FP32 accumulation in TMEM)
 // which leaves a relative error of about 2^-21 per product (the lo*lo term and
 // the rounding of lo), an order of magnitude inside the 1e-4 absolute bound the
@@ -59,57 +59,58 @@ __device__ __forceinline__ void tc_mma_tf32_pair(uint32_t d, uint64_t adesc, uin
 }
 
 // x -> (tf32(x), tf32(x - tf32(x))), both stored as FP32 words whose low 13
-// mantissa bits are zero.  n4 = number of float4 groups.
-__global__ void __launch_bounds__(256) split_tf32_kernel(const float4* __restrict__ x, float4* __restrict__ hi,
-                                                         float4* __restrict__ lo, long long n4) {
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-    const float4 v = __ldg(x + i);
-    const float in[4] = {v.x, v.y, v.z, v.w};
-    float h[4], l[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      uint32_t hb, lb;
-      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(in[k]));
-      h[k] = __uint_as_float(hb);
-      // Inf/NaN: keep them in the hi plane only (x - hi would be NaN)
-      const float d = isfinite(in[k]) ? __fsub_rn(in[k], h[k]) : 0.0f;
-      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(d));
-      l[k] = __uint_as_float(lb);
-    }
-    hi[i] = make_float4(h[0], h[1], h[2], h[3]);
-    lo[i] = make_float4(l[0], l[1], l[2], l[3]);
-  }
+// mantissa bits are zero.  Inf/NaN stay in the hi plane only (x - hi would be NaN).
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+  uint32_t hb, lb;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
+  hi = __uint_as_float(hb);
+  const float d = isfinite(x) ? __fsub_rn(x, hi) : 0.0f;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(d));
+  lo = __uint_as_float(lb);
 }
 
-// B[K, N] row-major -> the two planes of B^T, each [N, K] row-major (K contiguous).
-// 32 x 32 tiles through shared memory; blockDim = (32, 8).
-__global__ void __launch_bounds__(256) split_transpose_tf32_kernel(const float* __restrict__ b, float* __restrict__ hi_t,
-                                                                   float* __restrict__ lo_t, int K, int N) {
+// One launch splits both operands.  Blocks [0, blocks_a): A as it is stored, in
+// float4 groups (n4 of them) into the planes a_hi / a_lo.  The other blocks:
+// B[K, N] row-major into the two planes of B^T, each [N, K] row-major (K
+// contiguous), 32 x 32 tiles through shared memory.  256 threads per block.
+__global__ void __launch_bounds__(256) split_operands_kernel(const float4* __restrict__ a, float4* __restrict__ a_hi,
+                                                             float4* __restrict__ a_lo, long long n4, int blocks_a,
+                                                             const float* __restrict__ b, float* __restrict__ b_hi_t,
+                                                             float* __restrict__ b_lo_t, int K, int N) {
+  // the GEMM that consumes the planes may be scheduled as soon as SMs free up; it
+  // waits (griddepcontrol.wait) for this whole grid before its first load
+  asm volatile("griddepcontrol.launch_dependents;");
+  if ((int)blockIdx.x < blocks_a) {
+    const long long stride = (long long)blocks_a * 256;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < n4; i += stride) {
+      const float4 v = __ldg(a + i);
+      float4 h, l;
+      split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+      a_hi[i] = h;
+      a_lo[i] = l;
+    }
+    return;
+  }
   __shared__ float th[32][33], tl[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;      // 32 x 8
   const int tiles_n = (N + 31) / 32, tiles_k = (K + 31) / 32;
-  for (int t = blockIdx.x; t < tiles_n * tiles_k; t += gridDim.x) {
+  const int blocks_b = (int)gridDim.x - blocks_a;
+  for (int t = (int)blockIdx.x - blocks_a; t < tiles_n * tiles_k; t += blocks_b) {
     const int k0 = (t / tiles_n) * 32, n0 = (t % tiles_n) * 32;
 #pragma unroll
-    for (int r = threadIdx.y; r < 32; r += 8) {
-      const int k = k0 + r, n = n0 + threadIdx.x;
+    for (int r = ty; r < 32; r += 8) {
+      const int k = k0 + r, n = n0 + tx;
       float x = 0.0f;
       if (k < K && n < N) x = __ldg(b + (size_t)k * N + n);
-      uint32_t hb, lb;
-      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x));
-      const float h = __uint_as_float(hb);
-      const float d = isfinite(x) ? __fsub_rn(x, h) : 0.0f;
-      asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lb) : "f"(d));
-      th[r][threadIdx.x] = h;
-      tl[r][threadIdx.x] = __uint_as_float(lb);
+      split_tf32(x, th[r][tx], tl[r][tx]);
     }
     __syncthreads();
 #pragma unroll
-    for (int r = threadIdx.y; r < 32; r += 8) {
-      const int n = n0 + r, k = k0 + threadIdx.x;
+    for (int r = ty; r < 32; r += 8) {
+      const int n = n0 + r, k = k0 + tx;
       if (n < N && k < K) {
-        hi_t[(size_t)n * K + k] = th[threadIdx.x][r];
-        lo_t[(size_t)n * K + k] = tl[threadIdx.x][r];
+        b_hi_t[(size_t)n * K + k] = th[tx][r];
+        b_lo_t[(size_t)n * K + k] = tl[tx][r];
       }
     }
     __syncthreads();
@@ -182,6 +183,11 @@ gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmAh, const __grid_consta
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool ok = !*abort_flag;
+      // Launched as a programmatic dependent of the split kernel: everything above
+      // (barriers, TMEM, descriptor fetches) overlapped that kernel's tail; the
+      // planes it writes are read from here on.  Without the launch attribute this
+      // returns at once.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int tm, tn;
         tile_coords(tile, tiles_m2, tiles_n, tm, tn);
