@@ -911,12 +911,34 @@ __global__ void __launch_bounds__(THREADS) softmax_smem_row_kernel(const SmParam
   uint32_t it = 0;
   for (long long row = blockIdx.x; row < p.rows; row += gridDim.x, ++it) {
     const uint32_t b = it % (uint32_t)nbuf, parity = (it / (uint32_t)nbuf) & 1u;
-    if (!mbar_wait(bar0 + 8u * b, parity, abort_flag, status, kWdRowFull)) break;
     const uint32_t xs = s_rows + b * buf_bytes;
     const int len = valid_length<EXT>(p, row);
 
     if constexpr (UPT > 0) {
       // ---- register-resident form
+      // dropout decisions of this thread's units, four Philox blocks at a time: they
+      // depend on the row number only, so they are drawn while the row is still on its way
+      uint32_t km[UPT][4];
+      {
+        const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)L) >> 3;
+        constexpr int NB = UPT < 4 ? UPT : 4;
+#pragma unroll
+        for (int j0 = 0; j0 < UPT; j0 += NB) {
+          if (DROP) {
+            unsigned long long blk[NB];
+            uint32_t o[NB][4];
+#pragma unroll
+            for (int q = 0; q < NB; ++q) blk[q] = blk0 + (unsigned)(tid + (j0 + q) * THREADS);
+            philox_blocks<NB>(blk, p.key, o);
+#pragma unroll
+            for (int q = 0; q < NB; ++q) masks_from_words<true>(p, o[q], km[j0 + q]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < NB; ++q) masks_from_words<false>(p, km[j0 + q], km[j0 + q]);
+          }
+        }
+      }
+      if (!mbar_wait(bar0 + 8u * b, parity, abort_flag, status, kWdRowFull)) break;
       Unit<T> un[UPT];
       float m = -INFINITY;
 #pragma unroll
@@ -936,27 +958,6 @@ __global__ void __launch_bounds__(THREADS) softmax_smem_row_kernel(const SmParam
         if (nr < p.rows) {
           mbar_arrive_expect_tx(bar0 + 8u * b, row_bytes);
           stream::bulk_load(xs, in + nr * (long long)row_bytes, row_bytes, bar0 + 8u * b);
-        }
-      }
-      // dropout decisions of this thread's units, four Philox blocks at a time
-      uint32_t km[UPT][4];
-      {
-        const unsigned long long blk0 = ((p.first_row + (unsigned long long)row) * (unsigned long long)L) >> 3;
-        constexpr int NB = UPT < 4 ? UPT : 4;
-#pragma unroll
-        for (int j0 = 0; j0 < UPT; j0 += NB) {
-          if (DROP) {
-            unsigned long long blk[NB];
-            uint32_t o[NB][4];
-#pragma unroll
-            for (int q = 0; q < NB; ++q) blk[q] = blk0 + (unsigned)(tid + (j0 + q) * THREADS);
-            philox_blocks<NB>(blk, p.key, o);
-#pragma unroll
-            for (int q = 0; q < NB; ++q) masks_from_words<true>(p, o[q], km[j0 + q]);
-          } else {
-#pragma unroll
-            for (int q = 0; q < NB; ++q) masks_from_words<false>(p, km[j0 + q], km[j0 + q]);
-          }
         }
       }
       m = warp_max(m);
@@ -1007,6 +1008,7 @@ __global__ void __launch_bounds__(THREADS) softmax_smem_row_kernel(const SmParam
     }
 
     // ---- three sweeps over shared memory
+    if (!mbar_wait(bar0 + 8u * b, parity, abort_flag, status, kWdRowFull)) break;
     // sweep 1: maximum
     float m = -INFINITY;
     for (int u = tid; u < units; u += THREADS) {
