@@ -377,6 +377,7 @@ def run_gpu(args):
         others.update(side_workloads(tf, L, dev, peaks, args))
         if world == 1:
             others.update(reference_harness())
+            others.update(reference_gpu_kernels())
         if world == 1:
             v, rows, dt, threads = cpu_gemm_sample(12.0)
             cpu = {"value": v, "unit": "TFLOPS", "cores": threads, "kind": "port",
@@ -596,6 +597,27 @@ def reference_harness():
                                    "libtensorfuse.so: batch 32 x seq 128, 768 -> 3072 -> 768, FP32, 10 + 100 iterations"}}}
     except Exception as e:
         return {"reference_benchmark_error": repr(e)}
+
+
+def reference_gpu_kernels():
+    """The reference's own kernels (its C API + kernels compiled for sm_100a into
+    baseline/_ref/ref_lib/ by tests/ref_callers/build.py), timed in a process of their
+    own on configurations 2 and 4: the recompiled kernels this library replaces."""
+    runner = os.path.join(ROOT, "tests", "ref_callers", "run_reference_library.py")
+    lib = os.path.join(ROOT, "baseline", "_ref", "ref_lib", "libtensorfuse_reference.so")
+    if not (os.path.exists(runner) and os.path.exists(lib)):
+        return {}
+    try:
+        r = subprocess.run([sys.executable, runner, "bench"], capture_output=True, text=True, timeout=300)
+        lines = [x for x in r.stdout.splitlines() if x.startswith("{")]
+        if r.returncode != 0 or not lines:
+            return {"reference_gpu_kernels_error": (r.stdout + r.stderr)[-400:]}
+        res = json.loads(lines[-1])
+        res["note"] = ("the reference's kernels recompiled for sm_100a (CUTLASS mma.sync GEMM + separate bias/GELU kernel; "
+                       "one-thread-per-row softmax), same shapes, CUDA events, separate process; context only")
+        return {"reference_gpu_kernels": res}
+    except Exception as e:
+        return {"reference_gpu_kernels_error": repr(e)}
 
 
 def side_workloads(tf, L, dev, peaks, args):

@@ -12,7 +12,17 @@ include of the reference's headers (`#include "../tensorfuse/types.h"` in
 test_c_api_debug.cpp) is satisfied by a copy of this repository's
 include/tensorfuse/ placed where that path points.
 
-Outputs (all under baseline/_ref/ref_callers/, none of it version controlled):
+It also compiles the reference's own GPU library for sm_100a, from its sources
+where they lie in the checkout, into baseline/_ref/ref_lib/: the kernels this
+repository replaces, as a second comparator on a GPU (tests/test_reference_library_gpu.py,
+and the `reference_gpu_kernels` leg of bench.py).  That library needs NVIDIA
+CUTLASS headers, which the reference does not vendor; the recipe takes them from
+$CUTLASS_INCLUDE or from a Python package that ships them, and skips the step
+(recording why in the manifest) when there are none.
+
+Outputs (all under baseline/_ref/, none of it version controlled):
+    ref_lib/libtensorfuse_reference.so   the reference's library (optional, see above)
+  and under ref_callers/:
     bin/<program>               executables, rpath -> tensorfuse_b200/lib
     py/tensorfuse/*.py          the reference's pure-Python package, verbatim, plus a
                                 two-line _tensorfuse.py that re-exports this
@@ -66,6 +76,55 @@ def nvcc() -> str:
     return exe
 
 
+REF_LIB_DIR = os.path.join(ROOT, "baseline", "_ref", "ref_lib")
+REF_LIB = os.path.join(REF_LIB_DIR, "libtensorfuse_reference.so")
+REF_LIB_SOURCES = ["src/tensorfuse_c_api.cpp", "src/utils/error_handling.cpp", "src/kernels/fused_gemm_bias_gelu.cu",
+                   "src/kernels/fused_gemm_bias_gelu_int8.cu", "src/kernels/fused_gemm_bias_gelu_optimized.cu",
+                   "src/kernels/fused_softmax_dropout.cu"]
+
+
+def cutlass_include() -> str | None:
+    """A CUTLASS header tree: $CUTLASS_INCLUDE, else one shipped inside a Python package."""
+    env = os.environ.get("CUTLASS_INCLUDE")
+    if env and os.path.isdir(os.path.join(env, "cutlass")):
+        return env
+    import importlib.util
+    for pkg, rel in (("flashinfer", "data/cutlass/include"), ("tilelang", "3rdparty/cutlass/include")):
+        spec = importlib.util.find_spec(pkg)
+        if spec and spec.origin:
+            cand = os.path.join(os.path.dirname(spec.origin), rel)
+            if os.path.isdir(os.path.join(cand, "cutlass")):
+                return cand
+    return None
+
+
+def build_reference_library(reference: str, verbose: bool = True) -> dict:
+    """The reference's C API + kernels, compiled for sm_100a as they are (nothing is
+    copied or edited; only the shared library lands in baseline/_ref/ref_lib/)."""
+    info = {"ok": False, "path": REF_LIB, "sources": REF_LIB_SOURCES}
+    inc = cutlass_include()
+    if inc is None:
+        info["skipped"] = "no CUTLASS headers (set CUTLASS_INCLUDE)"
+        return info
+    os.makedirs(REF_LIB_DIR, exist_ok=True)
+    srcs = [os.path.join(reference, f) for f in REF_LIB_SOURCES]
+    if os.path.exists(REF_LIB) and all(os.path.getmtime(REF_LIB) > os.path.getmtime(f) for f in srcs):
+        info["ok"] = True
+        info["cached"] = True
+        return info
+    cmd = [nvcc(), "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "--expt-relaxed-constexpr",
+           "--expt-extended-lambda", "--use_fast_math", "-O3", "-w", "-Xcompiler", "-fPIC", "-shared",
+           "-I", os.path.join(reference, "src"), "-I", inc, "-o", REF_LIB, *srcs]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    info["ok"] = r.returncode == 0
+    info["cutlass_include"] = inc
+    if r.returncode:
+        info["log"] = (r.stdout + r.stderr)[-2000:]
+    if verbose:
+        print(("built  " if info["ok"] else "FAILED ") + "the reference's GPU library -> " + REF_LIB)
+    return info
+
+
 def build(reference: str, verbose: bool = True) -> dict:
     if not os.path.isdir(os.path.join(reference, "src", "tests")):
         raise RuntimeError(f"{reference} is not a checkout of the reference")
@@ -115,6 +174,7 @@ def build(reference: str, verbose: bool = True) -> dict:
     for f in PY_TESTS:
         shutil.copyfile(os.path.join(reference, "src", "tests", "python", f), os.path.join(tests, f))
         manifest["python"][f"tests/{f}"] = f"src/tests/python/{f}"
+    manifest["reference_library"] = build_reference_library(reference, verbose)
     with open(os.path.join(OUT, "manifest.json"), "w") as fh:
         json.dump(manifest, fh, indent=1)
     failed = [n for n, v in manifest["programs"].items() if not v["ok"]]
