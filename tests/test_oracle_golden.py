@@ -138,3 +138,43 @@ def test_fp16_gemm_single_rounding(oracle):
     got = oracle.gemm_bias_gelu_f16(A, B, b)
     want = oracle.np_gemm_bias_gelu(A.astype(np.float64), B.astype(np.float64), b.astype(np.float64))
     assert oracle.f16_ulp_distance(got, want.astype(np.float16)).max() <= 1
+
+
+# ------------------------------------------------- the reference's GPU kernels
+def _reference_gpu_golden():
+    import os
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, os.path.join(here, "golden"))
+    import gen_reference_gpu_golden as gen
+    if not os.path.exists(gen.GOLDEN):
+        pytest.skip("golden vectors of the reference's kernels absent")
+    c, g = gen.cases(), np.load(gen.GOLDEN)
+    assert bytes(g["inputs_sha256"]).decode() == gen.checksum(c)
+    return c, g
+
+
+def test_oracle_matches_outputs_of_the_reference_gpu_kernels(oracle):
+    """tests/golden/reference_gpu_kernels.npz holds what the reference's own library
+    (compiled from a checkout for sm_100a) wrote on a B200 for seeded operands
+    (tests/golden/gen_reference_gpu_golden.py).  The CPU oracle must agree with it:
+    FP32 GEMM at the reference's 1e-4; FP16 GEMM within 1e-2 relative + 1e-3 absolute
+    (the reference rounds the pre-activation to FP16, the oracle rounds once); INT8 in the
+    reference's scaled FP32 convention within 1e-3 of the largest magnitude (the reference
+    is built with --use_fast_math); softmax within 1e-4 / two FP16 ulps."""
+    c, g = _reference_gpu_golden()
+    got = oracle.gemm_bias_gelu_f32(c["gemm_f32_g/A"], c["gemm_f32_g/B"], c["gemm_f32_g/bias"])
+    assert np.abs(got - g["gemm_f32_g/C"]).max() < 1e-4
+    got = oracle.gemm_bias_gelu_f16(c["gemm_f16_g/A"], c["gemm_f16_g/B"], c["gemm_f16_g/bias"]).astype(np.float64)
+    theirs = g["gemm_f16_g/C"].astype(np.float64)
+    assert (np.abs(got - theirs) <= 1e-3 + 1e-2 * np.abs(theirs)).all()
+    sA, sB = (float(v) for v in c["gemm_i8_g/scales"])
+    acc = oracle.gemm_i8_acc(c["gemm_i8_g/A"], c["gemm_i8_g/B"])
+    got = oracle.i8_epilogue_legacy_f32(acc, c["gemm_i8_g/bias"], sA, sB)
+    theirs = g["gemm_i8_g/C"]
+    assert np.abs(got - theirs).max() <= 1e-3 * np.abs(theirs).max()
+    got = oracle.softmax_ref_f32(c["softmax_f32_g/x"])
+    assert np.abs(got - g["softmax_f32_g/out"]).max() < 1e-4
+    got = oracle.softmax_ref_f16(c["softmax_f16_g/x"])[0].astype(np.float64)
+    theirs = g["softmax_f16_g/out"].astype(np.float64)
+    assert (np.abs(got - theirs) <= 2.0 * np.maximum(np.abs(theirs) * 2.0 ** -10, 2.0 ** -24)).all()
