@@ -26,11 +26,14 @@
  *                                __expf and XORWOW and is not reproducible on a CPU; this
  *                                function is the reproducible statement of the same math.
  *
- * Parity status: the GELU/GEMM/softmax functions are pinned by the known-answer
- * values and the numpy-generated fixtures under tests/golden/ (produced by
- * importing the reference's own numpy oracle).  The FP16 and INT8 GEMM paths
- * have no numeric pin in the reference's tests ("parity unpinned" upstream);
- * they are pinned here only through the FP32 loop they share.
+ * Parity status: pinned.  The GELU/GEMM/softmax functions are held to the
+ * known-answer values of the reference's C++ tests, to the fixtures under
+ * tests/golden/ produced by importing the reference's own numpy oracle, and to
+ * outputs of the reference's own GPU kernels (its library compiled for sm_100a
+ * and run on a B200: tests/golden/reference_gpu_kernels.npz, FP32, FP16 and INT8
+ * GEMM and both softmax types).  The FP16 and INT8 GEMM paths have no numeric
+ * pin in the reference's own tests ("parity unpinned" upstream); those GPU
+ * outputs and the FP32 loop they share are what pins them here.
  *
  * Build: see oracle/Makefile (gcc -O2 -ffp-contract=off -fopenmp).
  */
