@@ -134,3 +134,54 @@ def test_dropout_statistics_match_the_reference_kernels(tf, reference_outputs):
         want = plain.astype(np.float64) / 0.8
         assert np.abs(o.astype(np.float64)[kept] - want[kept]).max() <= 2e-3, name
         assert (o[~kept] == 0).all(), name
+
+
+# ------------------------------------------------------------ benchmark sizes
+@pytest.fixture(scope="module")
+def reference_outputs_full(tmp_path_factory):
+    """The benchmark configurations themselves through the reference's kernels:
+    configuration 1 and 2 whole, a 1024-row band of configuration 3, a quarter of
+    the batch of configuration 4 (same generators, same seeds)."""
+    from tensorfuse_b200 import workloads
+    c = {}
+    x, w, b = workloads.gemm_fp32_quickstart()
+    c["gemm_f32_cfg1/A"], c["gemm_f32_cfg1/B"], c["gemm_f32_cfg1/bias"] = x.reshape(-1, x.shape[-1]), w, b
+    a, w, b = workloads.gemm_fp16_ffn(seed=1)
+    c["gemm_f16_cfg2/A"], c["gemm_f16_cfg2/B"], c["gemm_f16_cfg2/bias"] = a, w, b
+    a, w, b, sa, sw = workloads.gemm_int8(seed=2)
+    c["gemm_i8_cfg3/A"], c["gemm_i8_cfg3/B"], c["gemm_i8_cfg3/bias"] = a[:1024], w, b.astype(np.float32)
+    c["gemm_i8_cfg3/scales"] = np.array([1.0 / sa, 1.0 / sw], dtype=np.float32)    # the reference's q = x * scale
+    s = workloads.attention_scores(seed=3, batch=8, masked=True)
+    c["softmax_cfg4/x"], c["softmax_cfg4/p"], c["softmax_cfg4/seed"] = s, np.array([0.0], np.float32), np.array([3], np.uint64)
+    d = tmp_path_factory.mktemp("reflib_full")
+    src, dst = str(d / "in.npz"), str(d / "out.npz")
+    np.savez(src, **c)
+    r = subprocess.run([sys.executable, RUNNER, "cases", src, dst], capture_output=True, text=True, timeout=1200)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-3000:]
+    return c, np.load(dst)
+
+
+def test_benchmark_configurations_against_the_reference_kernels(tf, reference_outputs_full):
+    c, ref = reference_outputs_full
+    for g in ("gemm_f32_cfg1", "gemm_f16_cfg2", "gemm_i8_cfg3", "softmax_cfg4"):
+        assert int(ref[f"{g}/status"][0]) == 0, g
+    # configuration 1, whole output
+    mine = tf.fused_gemm_bias_gelu(c["gemm_f32_cfg1/A"], c["gemm_f32_cfg1/B"], c["gemm_f32_cfg1/bias"])
+    assert np.abs(mine - ref["gemm_f32_cfg1/C"]).max() < 1e-4
+    # configuration 2, whole output
+    mine = tf.fused_gemm_bias_gelu(c["gemm_f16_cfg2/A"], c["gemm_f16_cfg2/B"], c["gemm_f16_cfg2/bias"]).astype(np.float32)
+    theirs = ref["gemm_f16_cfg2/C"].astype(np.float32)
+    err = np.abs(mine - theirs)
+    assert (err <= 1e-3 + 1e-2 * np.abs(theirs)).all(), float(err.max())
+    # configuration 3, 1024 rows, the reference's scaled FP32 convention
+    sA, sB = (float(v) for v in c["gemm_i8_cfg3/scales"])
+    mine = tf.fused_gemm_bias_gelu(c["gemm_i8_cfg3/A"], c["gemm_i8_cfg3/B"], c["gemm_i8_cfg3/bias"], scales=(sA, sB),
+                                   out_dtype=np.float32)
+    theirs = ref["gemm_i8_cfg3/C"]
+    assert np.abs(mine - theirs).max() <= 1e-3 * np.abs(theirs).max()
+    # configuration 4 (8 of 32 batch items, key padding as -inf), p = 0
+    out, mask = tf.fused_softmax_dropout(c["softmax_cfg4/x"], dropout_prob=0.0)
+    theirs = ref["softmax_cfg4/out"].astype(np.float32)
+    err = np.abs(out.astype(np.float32) - theirs)
+    assert (err <= 2.0 * np.maximum(np.abs(theirs) * 2.0 ** -10, 2.0 ** -24)).all(), float(err.max())
+    assert ((out == 0) | (mask == 1)).all()
