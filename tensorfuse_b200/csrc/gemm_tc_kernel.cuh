@@ -136,7 +136,7 @@ __device__ __forceinline__ void staging_store16(uint32_t base, int row, int j, u
 
 // ------------------------------------------------------------ epilogue maths
 // Two neighbouring accumulators at once.  Fast path (FP16 output): packed
-// f32x2 arithmetic around the two MUFU operations per element of
+// f32x2 arithmetic around the special-function operations (three per pair) of
 // gelu(x) = x / (1 + 2^(-x (k1 + k2 x^2))).
 template <int EPI, bool FP32_OUT, bool INT_ACC>
 __device__ __forceinline__ float2 epilogue_pair(uint32_t r0, uint32_t r1, float b0, float b1, const EpiParams& ep) {
@@ -151,15 +151,20 @@ __device__ __forceinline__ float2 epilogue_pair(uint32_t r0, uint32_t r1, float 
     const float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
     const float k2 = k1 * 0.044715f;
     const uint64_t w2 = fma2(mul2(x2, x2), pack2(k2, k2), pack2(k1, k1));
-    const float2 nz = unpack2(mul2(x2, w2));     // -2u*log2(e)
+    float2 nz = unpack2(mul2(x2, w2));     // -2u*log2(e)
+    // One reciprocal serves the pair: 1/a = b/(ab), 1/b = a/(ab).  The special-function
+    // unit is what the epilogue is short of (three operations per pair instead of four);
+    // the exponent is capped at 60 so that the product of the two denominators stays
+    // finite (beyond it x * 2^-60 and the exact value both round to zero in 16 bits).
+    nz.x = fminf(nz.x, 60.0f);
+    nz.y = fminf(nz.y, 60.0f);
     float e0, e1;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(nz.x));
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(nz.y));
     const float2 d = unpack2(add2(pack2(e0, e1), pack2(1.0f, 1.0f)));
-    float q0, q1;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q0) : "f"(d.x));
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(q1) : "f"(d.y));
-    return unpack2(mul2(x2, pack2(q0, q1)));
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d.x * d.y));
+    return unpack2(mul2(x2, mul2(pack2(r, r), pack2(d.y, d.x))));
   } else {
     float2 o;
     if constexpr (INT_ACC) {
